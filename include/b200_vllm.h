@@ -678,10 +678,14 @@ void b200_runner_set_tp_fused(b200_runner*, int32_t on);
 #define B200_MIXER_DECAY_ATTN 4             /* linear attention with a decayed state (fixed or per-channel decay) */
 /* Layer layouts.  PARALLEL: mixer and feed-forward read ONE norm of the stream and add into it.  SANDWICH: every
  * sublayer has a norm before and after it: x += post_norm(mixer(norm(x))), then x += ff_post_norm(ff(ff_norm(x))).
- * In both a layer may have a SIDE mixer (b200_hybrid_set_layer_side) that reads the same normed input; the mixers'
+ * In all layouts a layer may have a SIDE mixer (b200_hybrid_set_layer_side) that reads the same normed input; the mixers'
  * outputs are summed, each times its out_scale.                                                                   */
 #define B200_LAYOUT_PARALLEL 0
 #define B200_LAYOUT_SANDWICH 1
+/* POSTNORM: a norm on each sublayer's OUTPUT only: x += post_norm(mixer(x)), then x += ff_post_norm(ff(x)); the
+ * sublayers read the stream itself (rounded to the operand dtype).  The feed-forward is the routed experts (with their
+ * shared expert) when experts > 0, else the dense gated feed-forward (shared_ff), as in SANDWICH.                  */
+#define B200_LAYOUT_POSTNORM 2
 
 void b200_resid_rmsnorm(void* out, const float* x, const float* w, int32_t num_tokens, int32_t width, float eps,
                         float w_offset, int32_t dt, int64_t stream);
@@ -713,6 +717,31 @@ void b200_window_attn(void* out, const float* q, const void* k_cache, const void
                       float scale, float softcap, int32_t dt, void* workspace, int64_t stream);
 int64_t b200_window_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t vdim,
                                          int32_t window, int32_t keep_first);
+/* Further options of the two calls above (a zeroed struct = the plain calls).
+ *   head_norm   != 0: q_norm_w / k_norm_w are fp32 [dim], shared by all heads, and every head is RMS-normed on its own
+ *   v_from_k    != 0: the projection row has no v block; the value row is the key row as projected (bias added, before
+ *                     the key norm and rotation), so vdim == dim
+ *   q_temp_coef, q_temp_every: every > 0: the query at position p is multiplied by
+ *                     1 + coef * ln(floor((p + 1) / every) + 1)                       (after norm and rotation)
+ *   dist_slopes fp32 [heads] or NULL: slope_h * (i - j) is taken off the score of query position i and key position j
+ *                     (after scale and cap)
+ *   gate_elems  != 0: the output gate has heads x vdim logits per token (one per output element) instead of heads   */
+typedef struct b200_attn_options {
+  int32_t head_norm, v_from_k, q_temp_every, gate_elems;
+  float q_temp_coef;
+  const float* dist_slopes;
+} b200_attn_options;
+void b200_window_attn_prep_ex(const float* proj, int32_t ld, const float* bias, const float* q_norm_w,
+                              const float* k_norm_w, const double* rot_freq, const int64_t* positions,
+                              const int64_t* slot_mapping, float* q_out, void* k_cache, void* v_cache,
+                              int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                              int32_t rot_dims, float eps, int32_t dt, const b200_attn_options* opt, int64_t stream);
+void b200_window_attn_ex(void* out, const float* q, const void* k_cache, const void* v_cache, const float* sink,
+                         const float* gate, int32_t ld_gate, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                         const uint32_t* block_tables, int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens,
+                         int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t window, int32_t keep_first,
+                         float scale, float softcap, int32_t dt, void* workspace, const b200_attn_options* opt,
+                         int64_t stream);
 /* out fp32 [T, channels] = sigmoid(bias + low w2^T)^(1 / tau); low fp32 [T, rank] (row stride ld_low), w2 fp32
  * [channels, rank], bias fp32 [channels] or NULL.                                                                  */
 void b200_lowrank_decay(float* out, const float* low, int32_t ld_low, const float* w2, const float* bias, float tau,
@@ -741,6 +770,18 @@ void b200_latent_attn(void* out, const float* q_full, const void* cache, const f
                       int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens, int32_t heads, int32_t kv_rank,
                       int32_t rot_dim, int32_t window, float scale, int32_t dt, void* workspace, int64_t stream);
 int64_t b200_latent_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_rank, int32_t window);
+/* b200_latent_prep for a layer that shares another layer's latent cache: qc holds the queries only, nothing is
+ * normed or written to a cache.                                                                                    */
+void b200_latent_prep_queries(const float* qc, int32_t ldq, void* q_plain, float* q_full, const double* rot_freq,
+                              float rot_mag, const int64_t* positions, int32_t num_tokens, int32_t heads, int32_t dim,
+                              int32_t rot_dim, int32_t rot_dims, int32_t kv_rank, int32_t dt, int64_t stream);
+/* b200_latent_attn with a per-head output gate: head h's output is multiplied by sigmoid(gate[t, h]), gate fp32
+ * [T, ld_gate] (NULL: none).                                                                                        */
+void b200_latent_attn_gated(void* out, const float* q_full, const void* cache, const float* sink, const float* gate,
+                            int32_t ld_gate, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                            const uint32_t* block_tables, int32_t max_blocks_per_seq, int32_t num_seqs,
+                            int32_t num_tokens, int32_t heads, int32_t kv_rank, int32_t rot_dim, int32_t window,
+                            float scale, int32_t dt, void* workspace, int64_t stream);
 /* Causal per-channel convolution + SiLU; state fp32 [slots, taps - 1, channels]; taps_w fp32 [channels, taps] (last
  * column = current token), bias fp32 [channels] or NULL.  out must not alias x (token chunks run in parallel).    */
 void b200_short_conv_silu(float* out, int32_t ldo, const float* x, int32_t ldx, const float* taps_w, const float* bias,
@@ -768,6 +809,22 @@ void b200_moe_experts(float* x, const void* h, const int32_t* top_idx, const flo
                       const void* w_down, int32_t num_tokens, int32_t experts, int32_t top, int32_t width, int32_t ff,
                       int32_t dt, void* workspace, int64_t stream);
 
+/* Router with a selection bias and expert groups.  s = softmax(logits) over all `experts` outputs; the choice score of
+ * expert e is s[e] + bias[e] (bias fp32 [experts] or NULL).  groups > 0: the outputs form `groups` equal runs of
+ * neighbours, a run's score is its largest choice score, and only members of the `keep` best runs can be chosen.  The
+ * `top` largest choice scores win (ties: lowest index); their weights are s (without the bias) times scale.       */
+void b200_moe_route_ex(const float* logits, const float* bias, int32_t num_tokens, int32_t experts, int32_t top,
+                       int32_t groups, int32_t keep, float scale, int32_t* top_idx, float* top_w, int64_t stream);
+/* b200_moe_experts with an activation kind and identity experts; out = (accumulate ? out : 0) + sum over a token's
+ * choices.  act 0: SiLU(gate) * up, w_up [E, 2 ff, width] (gate rows first); act 1: relu(up)^2, w_up [E, ff, width].
+ * Indices >= experts (up to experts + identity - 1) are identity experts: their output is the token's own input row,
+ * read from ident (fp32 when ident_f32 != 0, else dtype dt; [T, width]).  workspace: b200_moe_workspace_bytes with
+ * experts + identity.                                                                                              */
+void b200_moe_experts_ex(float* out, const void* h, const int32_t* top_idx, const float* top_w, const void* w_up,
+                         const void* w_down, int32_t num_tokens, int32_t experts, int32_t identity, int32_t top,
+                         int32_t width, int32_t ff, int32_t act, int32_t accumulate, const void* ident,
+                         int32_t ident_f32, int32_t dt, void* workspace, int64_t stream);
+
 typedef struct b200_hybrid_config {
   int32_t width, vocab, num_layers;
   int32_t dt;                               /* 0 = bf16 operands and cache, 1 = fp32 */
@@ -776,6 +833,8 @@ typedef struct b200_hybrid_config {
   int32_t num_state_slots;
   float norm_eps, norm_weight_offset;       /* layer / final norms multiply by (offset + w) */
   float embed_scale;                        /* the embedding row is multiplied by it */
+  float embed_pos_base;                     /* > 0: a sinusoidal position vector joins the embedding row: entry 2i is
+                                               sin(p base^(-2i / width)), entry 2i + 1 the cosine of the same angle */
 } b200_hybrid_config;
 
 typedef struct b200_hybrid_layer {
@@ -818,6 +877,21 @@ typedef struct b200_hybrid_layer {
   const void *w_decay2, *decay_bias;        /* fp32 [heads x dim, decay_rank], [heads x dim] */
   int32_t gated;                            /* window attention: != 0: per-head sigmoid output gate, logits last in w_in */
   void* v_cache;                            /* window attention: kv_cache holds K, v_cache V */
+  /* ---- POSTNORM layers, attention with a distance bias, shared latent caches, routers with groups
+   * gated (both attentions): 1 = one gate logit per head, 2 = one per output element (window attention only); the
+   * logits are the last rows of w_in.  w_in of a latent attention with shared_cache: the queries (and gate) only. */
+  int32_t head_norm, v_from_k;              /* window attention: see b200_attn_options */
+  int32_t q_temp_every;
+  float q_temp_coef;
+  const void* dist_slopes;                  /* fp32 [heads] or NULL */
+  int32_t shared_cache;                     /* latent attention: != 0: no latent projection of its own; kv_cache is
+                                               another (earlier) layer's cache, which this layer only reads */
+  int32_t expert_act, shared_act;           /* 0: SiLU(gate) * up ([gate | up] rows); 1: relu(up)^2 (up rows only) */
+  int32_t identity_experts;                 /* router outputs experts .. experts + identity_experts - 1 return the input */
+  int32_t route_groups, route_keep;         /* see b200_moe_route_ex (0: no groups) */
+  int32_t shared_gated;                     /* != 0: one more row closes w_shared_gate_up; the shared expert's output is
+                                               multiplied by the sigmoid of that row's product with the token */
+  const void* route_bias;                   /* fp32 [experts + identity_experts] or NULL */
 } b200_hybrid_layer;
 
 typedef struct b200_hybrid b200_hybrid;

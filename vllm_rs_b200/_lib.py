@@ -51,7 +51,14 @@ class HybridConfig(C.Structure):
 
     _fields_ = [(n, c_i32) for n in ("width", "vocab", "num_layers", "dt", "block_size", "num_blocks",
                                      "max_blocks_per_seq", "max_seqs", "max_tokens", "num_state_slots")] + \
-               [("norm_eps", c_f32), ("norm_weight_offset", c_f32), ("embed_scale", c_f32)]
+               [("norm_eps", c_f32), ("norm_weight_offset", c_f32), ("embed_scale", c_f32), ("embed_pos_base", c_f32)]
+
+
+class AttnOptions(C.Structure):
+    """b200_attn_options (include/b200_vllm.h)."""
+
+    _fields_ = [(n, c_i32) for n in ("head_norm", "v_from_k", "q_temp_every", "gate_elems")] + \
+               [("q_temp_coef", c_f32), ("dist_slopes", c_vp)]
 
 
 class HybridLayer(C.Structure):
@@ -69,7 +76,11 @@ class HybridLayer(C.Structure):
                [(n, c_f32) for n in ("softcap", "q_scale", "k_scale", "decay_tau", "out_scale")] + \
                [(n, c_vp) for n in ("post_norm_w", "ff_norm_w", "ff_post_norm_w", "in_bias", "o_bias", "q_norm_w",
                                     "k_norm_w", "head_decay", "w_decay2", "decay_bias")] + \
-               [("gated", c_i32), ("v_cache", c_vp)]
+               [("gated", c_i32), ("v_cache", c_vp)] + \
+               [("head_norm", c_i32), ("v_from_k", c_i32), ("q_temp_every", c_i32), ("q_temp_coef", c_f32),
+                ("dist_slopes", c_vp)] + \
+               [(n, c_i32) for n in ("shared_cache", "expert_act", "shared_act", "identity_experts", "route_groups",
+                                     "route_keep", "shared_gated")] + [("route_bias", c_vp)]
 
 
 class KvCachePlan(C.Structure):
@@ -244,16 +255,23 @@ _SIGS = {
     "b200_window_attn_prep": (None, [c_vp, c_i32] + [c_vp] * 9 + [c_i32] * 6 + [c_f32, c_i32, c_i64]),
     "b200_window_attn": (None, [c_vp] * 6 + [c_i32] + [c_vp] * 3 + [c_i32] * 9 + [c_f32, c_f32, c_i32, c_vp, c_i64]),
     "b200_window_attn_workspace_bytes": (c_i64, [c_i32] * 6),
+    "b200_window_attn_prep_ex": (None, [c_vp, c_i32] + [c_vp] * 9 + [c_i32] * 6 + [c_f32, c_i32, C.POINTER(AttnOptions), c_i64]),
+    "b200_window_attn_ex": (None, [c_vp] * 6 + [c_i32] + [c_vp] * 3 + [c_i32] * 9 + [c_f32, c_f32, c_i32, c_vp,
+                                                                                    C.POINTER(AttnOptions), c_i64]),
     "b200_lowrank_decay": (None, [c_vp, c_vp, c_i32, c_vp, c_vp, c_f32, c_i32, c_i32, c_i32, c_i64]),
     "b200_decay_attn": (None, [c_vp] * 4 + [c_i32, c_vp, c_vp, c_i32, c_f32, c_f32, c_i32] + [c_vp] * 4 + [c_i32] * 4 + [c_i64]),
     "b200_latent_prep": (None, [c_vp, c_i32] + [c_vp] * 5 + [c_f32, c_vp, c_vp] + [c_i32] * 6 + [c_f32, c_i32, c_i64]),
     "b200_latent_attn": (None, [c_vp] * 7 + [c_i32] * 7 + [c_f32, c_i32, c_vp, c_i64]),
     "b200_latent_attn_workspace_bytes": (c_i64, [c_i32] * 4),
+    "b200_latent_prep_queries": (None, [c_vp, c_i32, c_vp, c_vp, c_vp, c_f32, c_vp] + [c_i32] * 7 + [c_i64]),
+    "b200_latent_attn_gated": (None, [c_vp] * 5 + [c_i32] + [c_vp] * 3 + [c_i32] * 7 + [c_f32, c_i32, c_vp, c_i64]),
     "b200_short_conv_silu": (None, [c_vp, c_i32, c_vp, c_i32] + [c_vp] * 6 + [c_i32] * 4 + [c_i64]),
     "b200_delta_rule": (None, [c_vp] * 4 + [c_i32, c_vp, c_vp, c_i32] + [c_vp] * 6 + [c_i32] * 5 + [c_i64]),
     "b200_ssd_scan": (None, [c_vp] * 4 + [c_i32, c_vp, c_i32] + [c_vp] * 7 + [c_i32] * 5 + [c_i64]),
     "b200_moe_route": (None, [c_vp, c_i32, c_i32, c_i32, c_f32, c_vp, c_vp, c_i64]),
     "b200_moe_workspace_bytes": (c_i64, [c_i32] * 5),
+    "b200_moe_route_ex": (None, [c_vp, c_vp] + [c_i32] * 5 + [c_f32, c_vp, c_vp, c_i64]),
+    "b200_moe_experts_ex": (None, [c_vp] * 6 + [c_i32] * 8 + [c_vp, c_i32, c_i32, c_vp, c_i64]),
     "b200_moe_experts": (None, [c_vp] * 6 + [c_i32] * 6 + [c_vp, c_i64]),
     "b200_hybrid_new": (c_vp, [C.POINTER(HybridConfig)]),
     "b200_hybrid_free": (None, [c_vp]),

@@ -24,6 +24,9 @@
 // Sandwich layer (a norm before AND after each sublayer): the mixers of the layer (one, or two side by side with their
 // scales) write their sum into y, then x += post_norm(y) (resid_add_rmsnorm); the dense gated feed-forward reads
 // ff_norm(x), writes y, and x += ff_post_norm(y).
+// Post-norm layer (a norm on each sublayer's output only): the sublayers read the stream itself, rounded to the operand
+// dtype (cast_rows; fp32 runs read x in place): y = mixers(x), x += post_norm(y); y = ff(x), x += ff_post_norm(y), the
+// feed-forward being the routed experts (plus their shared expert) or the dense gated one.
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -58,6 +61,7 @@ struct b200_hybrid {
   float* x = nullptr;          // [T, width] residual stream
   float* y = nullptr;          // [T, width] output of a sublayer before the norm that follows it (sandwich layers)
   void* h = nullptr;           // [T, width] normed stream, operand dtype
+  const void* hin = nullptr;   // what the sublayers of the current layer read: h, or x itself (fp32 post-norm layers)
   float* proj = nullptr;       // [T, max fused input projection]
   float* conv = nullptr;       // [T, max convolved channels]: output of the short convolution
   float* aux = nullptr;        // [T, max(heads (kv_rank + rot_dim), heads vdim)] fp32: q_full / scan output / expanded values
@@ -109,9 +113,12 @@ static bool graphs_enabled() {
 
 static int in_rows(const b200_hybrid_layer& l) {
   switch (l.mixer) {
-    case B200_MIXER_LATENT_ATTN: return l.heads * (l.dim + l.rot_dim) + l.kv_rank + l.rot_dim;
+    case B200_MIXER_LATENT_ATTN:
+      return l.heads * (l.dim + l.rot_dim) + (l.shared_cache ? 0 : l.kv_rank + l.rot_dim) + (l.gated ? l.heads : 0);
     case B200_MIXER_DELTA_RULE: return 2 * l.kv_heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads;
-    case B200_MIXER_WINDOW_ATTN: return l.heads * l.dim + l.kv_heads * (l.dim + l.vdim) + (l.gated ? l.heads : 0);
+    case B200_MIXER_WINDOW_ATTN:
+      return l.heads * l.dim + l.kv_heads * (l.dim + (l.v_from_k ? 0 : l.vdim)) +
+             (l.gated == 2 ? l.heads * l.vdim : (l.gated ? l.heads : 0));
     case B200_MIXER_DECAY_ATTN: return 2 * l.heads * l.dim + 2 * l.heads * l.vdim + l.decay_rank;
     default: return 2 * l.heads * l.vdim + 2 * l.kv_heads * l.state + l.heads;
   }
@@ -152,11 +159,12 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
                                             : static_cast<size_t>(l.heads) * l.vdim + 2 * static_cast<size_t>(l.kv_heads) * l.state);
     }
     if (l.experts > 0) {
-      E = std::max<size_t>(E, l.experts);
+      E = std::max<size_t>(E, l.experts + l.identity_experts);
       top = std::max<size_t>(top, l.top);
-      moe_bytes = std::max<size_t>(moe_bytes, b200_moe_workspace_bytes(c.max_tokens, l.experts, l.top, c.width, l.expert_ff));
+      moe_bytes = std::max<size_t>(moe_bytes, b200_moe_workspace_bytes(c.max_tokens, l.experts + l.identity_experts,
+                                                                       l.top, c.width, l.expert_ff));
     }
-    sh_n = std::max<size_t>(sh_n, l.shared_ff);
+    sh_n = std::max<size_t>(sh_n, l.shared_ff + (l.shared_gated ? 1 : 0));
   }
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -222,7 +230,8 @@ static bool mixer_ok(const b200_hybrid_layer* l) {
   bool ok = l->heads > 0 && l->vdim > 0 && l->w_in && l->w_o;
   if (l->mixer == B200_MIXER_WINDOW_ATTN)
     return ok && l->kv_heads > 0 && l->heads % l->kv_heads == 0 && l->dim > 0 && l->rot_dims % 2 == 0 &&
-           l->rot_dims <= l->dim && (l->rot_dims == 0 || l->rot_freq) && l->kv_cache && l->v_cache;
+           l->rot_dims <= l->dim && (l->rot_dims == 0 || l->rot_freq) && l->kv_cache && l->v_cache &&
+           (!l->v_from_k || l->vdim == l->dim) && l->gated >= 0 && l->gated <= 2;
   if (l->mixer == B200_MIXER_DECAY_ATTN)
     return ok && l->dim > 0 && l->dim <= 256 && l->rec_state && l->norm_groups > 0 &&
            (l->heads * l->vdim) % l->norm_groups == 0 && (l->out_norm_period == 0 || l->out_norm_w) &&
@@ -246,16 +255,19 @@ void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_laye
     set_error(1, "hybrid_set_layer: layer out of range");
     return;
   }
-  bool ok = l->heads > 0 && l->vdim > 0 && l->norm_w && l->w_in && l->w_o;
+  bool ok = l->heads > 0 && l->vdim > 0 && l->w_in && l->w_o;
   if (l->layout == B200_LAYOUT_SANDWICH)
-    ok = ok && l->post_norm_w && l->experts == 0 && (l->shared_ff == 0 || (l->ff_norm_w && l->ff_post_norm_w));
+    ok = ok && l->norm_w && l->post_norm_w && l->experts == 0 && (l->shared_ff == 0 || (l->ff_norm_w && l->ff_post_norm_w));
+  else if (l->layout == B200_LAYOUT_POSTNORM)
+    ok = ok && l->post_norm_w && ((l->shared_ff == 0 && l->experts == 0) || l->ff_post_norm_w);
   else
-    ok = ok && l->layout == B200_LAYOUT_PARALLEL;
+    ok = ok && l->norm_w && l->layout == B200_LAYOUT_PARALLEL;
   if (l->mixer == B200_MIXER_WINDOW_ATTN || l->mixer == B200_MIXER_DECAY_ATTN)
     ok = ok && mixer_ok(l);
   else if (l->mixer == B200_MIXER_LATENT_ATTN)
-    ok = ok && l->kv_rank > 0 && l->w_uk && l->w_uv && l->latent_norm_w && l->kv_cache && l->rot_dims % 2 == 0 &&
-         l->rot_dims <= l->rot_dim && (l->rot_dims == 0 || l->rot_freq);
+    ok = ok && l->kv_rank > 0 && l->w_uk && l->w_uv && (l->shared_cache || l->latent_norm_w) && l->kv_cache &&
+         l->rot_dims % 2 == 0 && l->rot_dims <= l->rot_dim && (l->rot_dims == 0 || l->rot_freq) &&
+         (l->gated == 0 || l->gated == 1) && (!l->shared_cache || l->rot_dim == 0);
   else if (l->mixer == B200_MIXER_DELTA_RULE)
     ok = ok && l->kv_heads > 0 && l->heads % l->kv_heads == 0 && l->dim > 0 && l->conv_taps >= 1 && l->conv_w &&
          l->conv_state && l->rec_state && l->a_log && l->dt_bias && l->out_norm_w;
@@ -265,8 +277,18 @@ void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_laye
          (l->heads * l->vdim) % l->norm_groups == 0;
   else
     ok = false;
-  if (l->experts > 0) ok = ok && l->top > 0 && l->top <= l->experts && l->expert_ff > 0 && l->w_router && l->w_gate_up && l->w_down;
-  if (l->shared_ff > 0) ok = ok && l->w_shared_gate_up && l->w_shared_down;
+  if (l->experts > 0) {
+    const int all = l->experts + l->identity_experts;
+    ok = ok && l->identity_experts >= 0 && l->top > 0 && l->top <= all && l->expert_ff > 0 && l->w_router &&
+         l->w_gate_up && l->w_down && (l->expert_act == 0 || l->expert_act == 1) && l->route_groups >= 0 &&
+         (l->route_groups == 0 || (all % l->route_groups == 0 && l->route_keep >= 1 && l->route_keep <= l->route_groups &&
+                                   l->top <= all / l->route_groups * l->route_keep));
+  } else {
+    ok = ok && l->identity_experts == 0;
+  }
+  if (l->shared_ff > 0)
+    ok = ok && l->w_shared_gate_up && l->w_shared_down && (l->shared_act == 0 || l->shared_act == 1) &&
+         (!l->shared_gated || l->shared_act == 1);
   if (!ok) {
     set_error(1, "hybrid_set_layer: inconsistent layer description");
     return;
@@ -332,17 +354,20 @@ static void mixer_latent(b200_hybrid* r, const b200_hybrid_layer& l, const int64
                          float* dst, float alpha, float beta, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, R = l.kv_rank + l.rot_dim, n_in = in_rows(l);
-  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
-  launch_latent_prep(r->proj, n_in, r->opa, r->aux, l.kv_cache, (const float*)l.latent_norm_w, l.rot_freq, l.rot_mag,
-                     positions, slots, T, H, l.dim, l.rot_dim, l.rot_dims, l.kv_rank, c.norm_eps, c.dt, st);
+  gemm_f32out(r->hin, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  // a layer that shares another layer's cache brings queries only: nothing is normed or written
+  launch_latent_prep(r->proj, n_in, r->opa, r->aux, l.shared_cache ? nullptr : l.kv_cache, (const float*)l.latent_norm_w,
+                     l.rot_freq, l.rot_mag, positions, slots, T, H, l.dim, l.rot_dim, l.rot_dims, l.kv_rank, c.norm_eps,
+                     c.dt, st);
   // q_abs[t, h, :] = q_plain[t, h, :] W_uk[h]  (W_uk[h] is [dim, kv_rank], i.e. stored [K, N])
   if (l.dim > 0)
     gemm_f32out(r->opa, H * l.dim, l.dim, l.w_uk, l.kv_rank, static_cast<long long>(l.dim) * l.kv_rank, r->aux, H * R, R,
                 T, l.kv_rank, l.dim, H, 0.f, 1, c.dt, st);
   else
     cudaMemsetAsync(r->aux, 0, static_cast<size_t>(T) * H * R * 4, st);   // (rotated parts are rewritten by prep; dim == 0 is rejected upstream)
-  launch_latent_attn(r->lat, r->aux, l.kv_cache, (const float*)l.sink, cu, ctx, bt, max_blocks, B, T, H, l.kv_rank,
-                     l.rot_dim, l.window, l.scale, c.dt,
+  const float* gate = l.gated ? r->proj + (n_in - H) : nullptr;          // the gate logits close the projection row
+  launch_latent_attn(r->lat, r->aux, l.kv_cache, (const float*)l.sink, gate, n_in, cu, ctx, bt, max_blocks, B, T, H,
+                     l.kv_rank, l.rot_dim, l.window, l.scale, c.dt,
                      static_cast<size_t>(T) <= r->attn_ws_rows ? r->attn_ws : nullptr, st);
   // v[t, h, :] = lat[t, h, :] W_uv[h]^T  (W_uv[h] is [vdim, kv_rank])
   gemm_f32out(r->lat, H * l.kv_rank, l.kv_rank, l.w_uv, l.kv_rank, static_cast<long long>(l.vdim) * l.kv_rank, r->aux,
@@ -361,7 +386,7 @@ static void mixer_delta(b200_hybrid* r, const b200_hybrid_layer& l, const uint32
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, Hk = l.kv_heads, n_in = in_rows(l);
   const int nq = Hk * l.dim, nv = H * l.vdim, nconv = 2 * nq + nv;
-  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  gemm_f32out(r->hin, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
   launch_short_conv_silu(r->conv, nconv, r->proj, n_in, (const float*)l.conv_w, (const float*)l.conv_b,
                          (float*)l.conv_state, state_slots, cu, ctx, B, T, nconv, l.conv_taps, st);
   const float* q = r->conv;
@@ -382,7 +407,7 @@ static void mixer_ssd(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, G = l.kv_heads, N = l.state, inner = H * l.vdim, n_in = in_rows(l);
   const int nconv = inner + 2 * G * N;
-  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  gemm_f32out(r->hin, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
   const float* xbc = r->conv;
   launch_short_conv_silu(r->conv, nconv, r->proj + inner, n_in, (const float*)l.conv_w, (const float*)l.conv_b,
                          (float*)l.conv_state, state_slots, cu, ctx, B, T, nconv, l.conv_taps, st);
@@ -399,14 +424,21 @@ static void mixer_window(b200_hybrid* r, const b200_hybrid_layer& l, const int64
                          float* dst, float alpha, float beta, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, G = l.kv_heads, n_in = in_rows(l), nv = H * l.vdim;
-  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  gemm_f32out(r->hin, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  b200_attn_options opt;
+  opt.head_norm = l.head_norm;
+  opt.v_from_k = l.v_from_k;
+  opt.q_temp_every = l.q_temp_every;
+  opt.q_temp_coef = l.q_temp_coef;
+  opt.gate_elems = l.gated == 2;
+  opt.dist_slopes = (const float*)l.dist_slopes;
   launch_window_attn_prep(r->proj, n_in, (const float*)l.in_bias, (const float*)l.q_norm_w, (const float*)l.k_norm_w,
                           l.rot_freq, positions, slots, r->aux, l.kv_cache, l.v_cache, T, H, G, l.dim, l.vdim, l.rot_dims,
-                          c.norm_eps, c.dt, st);
-  const float* gate = l.gated ? r->proj + H * l.dim + G * (l.dim + l.vdim) : nullptr;
+                          c.norm_eps, c.dt, &opt, st);
+  const float* gate = l.gated ? r->proj + H * l.dim + G * (l.dim + (l.v_from_k ? 0 : l.vdim)) : nullptr;
   launch_window_attn(r->opa, r->aux, l.kv_cache, l.v_cache, (const float*)l.sink, gate, n_in, cu, ctx, bt, max_blocks, B,
                      T, H, G, l.dim, l.vdim, l.window, l.keep_first, l.scale, l.softcap, c.dt,
-                     static_cast<size_t>(T) <= r->attn_ws_rows ? r->attn_ws : nullptr, st);
+                     static_cast<size_t>(T) <= r->attn_ws_rows ? r->attn_ws : nullptr, &opt, st);
   gemm_f32out_scaled(r->opa, nv, 0, l.w_o, nv, 0, dst, c.width, 0, T, c.width, nv, 1, alpha, beta, 0, c.dt, st);
   if (l.o_bias) launch_bias_rows(dst, (const float*)l.o_bias, alpha, T, c.width, st);
 }
@@ -415,7 +447,7 @@ static void mixer_decay(b200_hybrid* r, const b200_hybrid_layer& l, const uint32
                         const int32_t* state_slots, int B, int T, float* dst, float alpha, float beta, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, nk = H * l.dim, nv = H * l.vdim, n_in = in_rows(l);
-  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  gemm_f32out(r->hin, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
   const float* q = r->proj;
   const float* k = q + nk;
   const float* v = k + nk;
@@ -455,28 +487,38 @@ static void run_mixer(b200_hybrid* r, const b200_hybrid_layer& l, const int64_t*
 // dense gated feed-forward of a sandwich layer: y = W_down (silu(W_gate h) * (W_up h))
 static void dense_ffn(b200_hybrid* r, const b200_hybrid_layer& l, int T, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
-  gemm_f32out(r->h, c.width, 0, l.w_shared_gate_up, c.width, 0, r->sh, 2 * l.shared_ff, 0, T, 2 * l.shared_ff, c.width, 1,
+  gemm_f32out(r->hin, c.width, 0, l.w_shared_gate_up, c.width, 0, r->sh, 2 * l.shared_ff, 0, T, 2 * l.shared_ff, c.width, 1,
               0.f, 0, c.dt, st);
   launch_silu_mul_f32(r->sha, r->sh, T, l.shared_ff, c.dt, st);
   gemm_f32out(r->sha, l.shared_ff, 0, l.w_shared_down, l.shared_ff, 0, r->y, c.width, 0, T, c.width, l.shared_ff, 1, 0.f,
               0, c.dt, st);
 }
 
-static void feed_forward(b200_hybrid* r, const b200_hybrid_layer& l, int T, cudaStream_t st) {
+// routed experts and their shared expert: dst = (accumulate ? dst : 0) + experts(h) + shared(h).  `ident` / `ident_f32`:
+// the rows that identity experts return (the sublayer's input before any rounding, where the layer has it in fp32).
+static void feed_forward(b200_hybrid* r, const b200_hybrid_layer& l, int T, float* dst, bool accumulate, const void* ident,
+                         int ident_f32, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   if (l.experts > 0) {
-    gemm_f32out(r->h, c.width, 0, l.w_router, c.width, 0, r->rlog, l.experts, 0, T, l.experts, c.width, 1, 0.f, 0, c.dt,
-                st);
-    launch_moe_route(r->rlog, T, l.experts, l.top, l.route_scale, r->top_idx, r->top_w, st);
-    b200_moe_experts(r->x, r->h, r->top_idx, r->top_w, l.w_gate_up, l.w_down, T, l.experts, l.top, c.width, l.expert_ff,
-                     c.dt, r->moe_ws, reinterpret_cast<int64_t>(st));
+    const int all = l.experts + l.identity_experts;
+    gemm_f32out(r->hin, c.width, 0, l.w_router, c.width, 0, r->rlog, all, 0, T, all, c.width, 1, 0.f, 0, c.dt, st);
+    launch_moe_route(r->rlog, (const float*)l.route_bias, T, all, l.top, l.route_groups, l.route_keep, l.route_scale,
+                     r->top_idx, r->top_w, st);
+    b200_moe_experts_ex(dst, r->hin, r->top_idx, r->top_w, l.w_gate_up, l.w_down, T, l.experts, l.identity_experts, l.top,
+                        c.width, l.expert_ff, l.expert_act, accumulate ? 1 : 0, ident, ident_f32, c.dt, r->moe_ws,
+                        reinterpret_cast<int64_t>(st));
+    accumulate = true;
   }
   if (l.shared_ff > 0) {
-    gemm_f32out(r->h, c.width, 0, l.w_shared_gate_up, c.width, 0, r->sh, 2 * l.shared_ff, 0, T, 2 * l.shared_ff, c.width,
-                1, 0.f, 0, c.dt, st);
-    launch_silu_mul_f32(r->sha, r->sh, T, l.shared_ff, c.dt, st);
-    gemm_f32out(r->sha, l.shared_ff, 0, l.w_shared_down, l.shared_ff, 0, r->x, c.width, 0, T, c.width, l.shared_ff, 1,
-                1.f, 0, c.dt, st);
+    // SiLU-gated: [gate | up] rows; squared ReLU: up rows, closed by the one row of the token's gate where there is one
+    const int rows = l.shared_act == 0 ? 2 * l.shared_ff : l.shared_ff + (l.shared_gated ? 1 : 0);
+    gemm_f32out(r->hin, c.width, 0, l.w_shared_gate_up, c.width, 0, r->sh, rows, 0, T, rows, c.width, 1, 0.f, 0, c.dt, st);
+    if (l.shared_act == 0)
+      launch_silu_mul_f32(r->sha, r->sh, T, l.shared_ff, c.dt, st);
+    else
+      launch_relu2_f32(r->sha, r->sh, rows, T, l.shared_ff, l.shared_gated ? l.shared_ff : -1, c.dt, st);
+    gemm_f32out(r->sha, l.shared_ff, 0, l.w_shared_down, l.shared_ff, 0, dst, c.width, 0, T, c.width, l.shared_ff, 1,
+                accumulate ? 1.f : 0.f, 0, c.dt, st);
   }
 }
 
@@ -495,10 +537,36 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long launches0 = launch_count();
-  launch_embed_f32(r->x, r->embed, input_ids, T, c.width, c.vocab, c.embed_scale, c.dt, st);
+  launch_embed_f32(r->x, r->embed, input_ids, positions, c.embed_pos_base, T, c.width, c.vocab, c.embed_scale, c.dt, st);
   for (int i = 0; i < c.num_layers; ++i) {
     const b200_hybrid_layer& l = r->layers[i];
     const b200_hybrid_layer& side = r->sides[i];
+    r->hin = r->h;
+    if (l.layout == B200_LAYOUT_POSTNORM) {
+      // the sublayers read the stream itself: rounded to bf16 for the products, in place for fp32 runs
+      auto stream_in = [&]() {
+        if (c.dt) r->hin = r->x;
+        else launch_cast_rows(r->h, r->x, c.width, T, c.width, 0, st);
+      };
+      stream_in();
+      run_mixer(r, l, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->y, l.out_scale,
+                0.f, st);
+      if (side.heads > 0)
+        run_mixer(r, side, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->y,
+                  side.out_scale, 1.f, st);
+      launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.post_norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, st);
+      if (l.experts > 0 || l.shared_ff > 0) {
+        stream_in();
+        if (l.experts > 0) feed_forward(r, l, T, r->y, false, r->x, 1, st);
+        else dense_ffn(r, l, T, st);
+        launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.ff_post_norm_w, T, c.width, c.norm_eps,
+                                 c.norm_weight_offset, st);
+      }
+      if (r->trace)
+        cudaMemcpyAsync(r->trace + static_cast<size_t>(i) * c.max_tokens * c.width, r->x,
+                        static_cast<size_t>(T) * c.width * 4, cudaMemcpyDeviceToDevice, st);
+      continue;
+    }
     launch_resid_rmsnorm(r->h, r->x, (const float*)l.norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, nullptr,
                          c.dt, st);
     if (l.layout == B200_LAYOUT_SANDWICH) {
@@ -521,7 +589,7 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
       if (side.heads > 0)
         run_mixer(r, side, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->x,
                   side.out_scale, 1.f, st);
-      feed_forward(r, l, T, st);
+      feed_forward(r, l, T, r->x, true, r->h, 0, st);
     }
     if (r->trace)
       cudaMemcpyAsync(r->trace + static_cast<size_t>(i) * c.max_tokens * c.width, r->x,

@@ -9,7 +9,9 @@
 // and the kernel returns the attention-weighted LATENT sum_j p_j c_j [T, H, kv_rank]; the runner expands it with
 // W_uv[h].  All heads of a token read the same cache rows (multi-query form), which is what makes the latent cache
 // cheap to stream.  Options: sliding window (position i sees j with 0 <= i - j < window; window <= 0 = all), and a
-// learned per-head sink logit that joins the softmax denominator without a key or value.
+// learned per-head sink logit that joins the softmax denominator without a key or value, and a per-head output gate
+// (head h's result times sigmoid(gate[t, h]); the gate commutes with the value expansion that follows).  A layer may
+// read ANOTHER layer's cache (latent_prep with no cache: queries only), with its own W_uk / W_uv folded in around it.
 // Two kernels: an fp32 FMA form (any sizes, both dtypes; rows of small steps split their keys over several blocks and
 // merge) and a bf16 tensor-core form for steps of many rows (kv_rank a multiple of 64 up to 512, kv_rank + rot_dim a
 // multiple of 16).  Beside paged_attn_decode.cu / attn_prefill*.cu (per-head K / V caches, fp16 / bf16, no window
@@ -42,6 +44,7 @@ __global__ void latent_prep_kernel(const float* __restrict__ qc, int ldq, T* __r
   float* red = sm + 2 * half;
   const int t = blockIdx.x;
   const float* row = qc + static_cast<size_t>(t) * ldq;
+  const bool own_latent = cache != nullptr;            // otherwise the row holds the queries only
   const float* craw = row + static_cast<size_t>(heads) * (dim + rot_dim);
   const float* kraw = craw + kv_rank;
   const double pos = static_cast<double>(positions[t]);
@@ -52,10 +55,11 @@ __global__ void latent_prep_kernel(const float* __restrict__ qc, int ldq, T* __r
     sn[i] = static_cast<float>(s) * rot_mag;
   }
   float ss = 0.f;
-  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) ss += craw[d] * craw[d];
+  if (own_latent)
+    for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) ss += craw[d] * craw[d];
   ss = block_sum(ss, red);           // also orders the cos / sin writes before their use
   const float inv = 1.f / sqrtf(ss / static_cast<float>(kv_rank) + eps);
-  const int64_t slot = slots[t];
+  const int64_t slot = own_latent ? slots[t] : -1;
   const int R = kv_rank + rot_dim;
   if (slot >= 0) {
     T* crow = cache + static_cast<size_t>(slot) * R;
@@ -93,11 +97,11 @@ __global__ void latent_prep_kernel(const float* __restrict__ qc, int ldq, T* __r
 // in shared memory (fp32) and used by every head of the group.
 template <typename T>
 __global__ void latent_attn_kernel(T* __restrict__ out, const float* __restrict__ q_full, const T* __restrict__ cache,
-                                   const float* __restrict__ sink, const uint32_t* __restrict__ cu,
-                                   const uint32_t* __restrict__ ctx, const uint32_t* __restrict__ block_tables,
-                                   int max_blocks, int num_seqs, int heads, int kv_rank, int rot_dim, int window,
-                                   float scale, int key_tile, int nsplit, float* __restrict__ part_o,
-                                   float* __restrict__ part_ml) {
+                                   const float* __restrict__ sink, const float* __restrict__ gate, int ld_gate,
+                                   const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
+                                   const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads,
+                                   int kv_rank, int rot_dim, int window, float scale, int key_tile, int nsplit,
+                                   float* __restrict__ part_o, float* __restrict__ part_ml) {
   extern __shared__ float sm[];
   const int R = kv_rank + rot_dim, Rp = R | 1;        // odd row pitch: a lane per key reads conflict-free
   const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -167,7 +171,8 @@ __global__ void latent_attn_kernel(T* __restrict__ out, const float* __restrict_
     }
   }
   if (live && nsplit == 1) {
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    if (gate) inv *= sigmoid_f(gate[static_cast<size_t>(t) * ld_gate + h]);
     T* o = out + (static_cast<size_t>(t) * heads + h) * kv_rank;
     for (int d = lane; d < kv_rank; d += 32) st(o + d, os[warp * kv_rank + d] * inv);
   } else if (live) {
@@ -183,8 +188,9 @@ __global__ void latent_attn_kernel(T* __restrict__ out, const float* __restrict_
 // one block per (token, head): the parts of a split run and the sink meet in one softmax
 template <typename T>
 __global__ void latent_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml, const float* __restrict__ sink, int heads,
-                                         int kv_rank, int nsplit) {
+                                         const float* __restrict__ part_ml, const float* __restrict__ sink,
+                                         const float* __restrict__ gate, int ld_gate, int heads, int kv_rank,
+                                         int nsplit) {
   const size_t th = blockIdx.x;
   const int h = static_cast<int>(th % heads);
   const float* ml = part_ml + th * nsplit * 2;
@@ -192,7 +198,8 @@ __global__ void latent_attn_merge_kernel(T* __restrict__ out, const float* __res
   for (int z = 0; z < nsplit; ++z) m = fmaxf(m, ml[2 * z]);
   float l = sink ? expf(sink[h] - m) : 0.f;
   for (int z = 0; z < nsplit; ++z) l += ml[2 * z + 1] * expf(ml[2 * z] - m);
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  if (gate) inv *= sigmoid_f(gate[(th / heads) * ld_gate + h]);
   for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
     float acc = 0.f;
     for (int z = 0; z < nsplit; ++z) acc += part_o[(th * nsplit + z) * kv_rank + d] * expf(ml[2 * z] - m);
@@ -241,6 +248,7 @@ template <int NT, bool HROWS>
 __global__ void __launch_bounds__(128)
 latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ q_full,
                        const __nv_bfloat16* __restrict__ cache, const float* __restrict__ sink,
+                       const float* __restrict__ gate, int ld_gate,
                        const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
                        const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_rank,
                        int rot_dim, int window, float scale, int nsplit, float* __restrict__ part_o,
@@ -400,12 +408,14 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
       }
     }
   }
-  const float inv[2] = {l[0] > 0.f ? 1.f / l[0] : 0.f, l[1] > 0.f ? 1.f / l[1] : 0.f};
+  float inv[2] = {l[0] > 0.f ? 1.f / l[0] : 0.f, l[1] > 0.f ? 1.f / l[1] : 0.f};
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
     const int r = g + rr * 8;
     if (r >= nrows) continue;
     const size_t orow = HROWS ? static_cast<size_t>(row0) * heads + h + r : static_cast<size_t>(row0 + r) * heads + h;
+    if (gate && nsplit == 1)            // orow = token row * heads + head
+      inv[rr] *= sigmoid_f(gate[(orow / heads) * ld_gate + (orow % heads)]);
     if (nsplit == 1) {
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
@@ -451,7 +461,7 @@ static int latent_attn_mma_splits(int T, int heads, int window) {
 }
 // true when the tensor-core kernel took the step.  hrows: steps of few rows (heads as MMA rows, keys split).
 static bool launch_latent_attn_mma(void* out, const float* q_full, const void* cache, const float* sink,
-                                   const uint32_t* cu, const uint32_t* ctx, const uint32_t* block_tables, int max_blocks,
+                                   const float* gate, int ld_gate, const uint32_t* cu, const uint32_t* ctx, const uint32_t* block_tables, int max_blocks,
                                    int num_seqs, int T, int heads, int kv_rank, int rot_dim, int window, float scale,
                                    bool hrows, void* workspace, cudaStream_t st_) {
   const int R = kv_rank + rot_dim;
@@ -465,9 +475,9 @@ static bool launch_latent_attn_mma(void* out, const float* q_full, const void* c
   {                                                                                                                \
     auto kern = latent_attn_mma_kernel<NT, HR>;                                                                    \
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));               \
-    kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q_full, (const __nv_bfloat16*)cache, sink, cu, ctx,        \
-                                   block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale,     \
-                                   nsplit, part_o, part_ml);                                                       \
+    kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q_full, (const __nv_bfloat16*)cache, sink, gate, ld_gate,  \
+                                   cu, ctx, block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window,   \
+                                   scale, nsplit, part_o, part_ml);                                                \
   }
 #define B200_LMMA(NT)                 \
   if (hrows) B200_LMMA2(NT, true)     \
@@ -488,7 +498,7 @@ static bool launch_latent_attn_mma(void* out, const float* q_full, const void* c
   B200_CUDA_LAUNCH_CHECK();
   if (nsplit > 1) {
     latent_attn_merge_kernel<__nv_bfloat16><<<T * heads, kv_rank >= 256 ? 256 : 128, 0, st_>>>(
-        (__nv_bfloat16*)out, part_o, part_ml, sink, heads, kv_rank, nsplit);
+        (__nv_bfloat16*)out, part_o, part_ml, sink, gate, ld_gate, heads, kv_rank, nsplit);
     B200_CUDA_LAUNCH_CHECK();
   }
   return true;
@@ -506,13 +516,13 @@ size_t latent_attn_workspace_bytes(int T, int heads, int kv_rank, int window) {
   return n == 1 ? 0 : static_cast<size_t>(T) * heads * n * (kv_rank + 2) * 4;
 }
 
-void launch_latent_attn(void* out, const float* q_full, const void* cache, const float* sink, const uint32_t* cu,
-                        const uint32_t* ctx, const uint32_t* block_tables, int max_blocks, int num_seqs, int T,
-                        int heads, int kv_rank, int rot_dim, int window, float scale, int dt, void* workspace,
-                        cudaStream_t st_) {
+void launch_latent_attn(void* out, const float* q_full, const void* cache, const float* sink, const float* gate,
+                        int ld_gate, const uint32_t* cu, const uint32_t* ctx, const uint32_t* block_tables,
+                        int max_blocks, int num_seqs, int T, int heads, int kv_rank, int rot_dim, int window, float scale,
+                        int dt, void* workspace, cudaStream_t st_) {
   if (T <= 0) return;
   // steps of many rows in bf16: the tensor-core kernel (small steps keep the split form below)
-  if (!dt && launch_latent_attn_mma(out, q_full, cache, sink, cu, ctx, block_tables, max_blocks, num_seqs, T, heads,
+  if (!dt && launch_latent_attn_mma(out, q_full, cache, sink, gate, ld_gate, cu, ctx, block_tables, max_blocks, num_seqs, T, heads,
                                     kv_rank, rot_dim, window, scale, /*hrows=*/T <= 2 * sm_count() / 4, workspace, st_))
     return;
   const int R = kv_rank + rot_dim, Rp = R | 1;
@@ -533,25 +543,25 @@ void launch_latent_attn(void* out, const float* q_full, const void* cache, const
   if (dt) {
     auto kern = latent_attn_kernel<float>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    kern<<<grid, nw * 32, smem, st_>>>((float*)out, q_full, (const float*)cache, sink, cu, ctx, block_tables,
-                                       max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale, key_tile, nsplit,
-                                       part_o, part_ml);
+    kern<<<grid, nw * 32, smem, st_>>>((float*)out, q_full, (const float*)cache, sink, gate, ld_gate, cu, ctx,
+                                       block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale,
+                                       key_tile, nsplit, part_o, part_ml);
   } else {
     auto kern = latent_attn_kernel<__nv_bfloat16>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    kern<<<grid, nw * 32, smem, st_>>>((__nv_bfloat16*)out, q_full, (const __nv_bfloat16*)cache, sink, cu, ctx,
-                                       block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale,
-                                       key_tile, nsplit, part_o, part_ml);
+    kern<<<grid, nw * 32, smem, st_>>>((__nv_bfloat16*)out, q_full, (const __nv_bfloat16*)cache, sink, gate, ld_gate,
+                                       cu, ctx, block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window,
+                                       scale, key_tile, nsplit, part_o, part_ml);
   }
   B200_CUDA_LAUNCH_CHECK();
   if (nsplit > 1) {
     const int th = kv_rank >= 256 ? 256 : 128;
     if (dt)
-      latent_attn_merge_kernel<float><<<T * heads, th, 0, st_>>>((float*)out, part_o, part_ml, sink, heads, kv_rank,
-                                                                 nsplit);
+      latent_attn_merge_kernel<float><<<T * heads, th, 0, st_>>>((float*)out, part_o, part_ml, sink, gate, ld_gate,
+                                                                 heads, kv_rank, nsplit);
     else
       latent_attn_merge_kernel<__nv_bfloat16><<<T * heads, th, 0, st_>>>((__nv_bfloat16*)out, part_o, part_ml, sink,
-                                                                         heads, kv_rank, nsplit);
+                                                                         gate, ld_gate, heads, kv_rank, nsplit);
     B200_CUDA_LAUNCH_CHECK();
   }
 }
@@ -563,7 +573,7 @@ void b200_latent_prep(const float* qc, int32_t ldq, void* q_plain, float* q_full
                       const float* latent_norm_w, const double* rot_freq, float rot_mag, const int64_t* positions,
                       const int64_t* slot_mapping, int32_t num_tokens, int32_t heads, int32_t dim, int32_t rot_dim,
                       int32_t rot_dims, int32_t kv_rank, float eps, int32_t dt, int64_t stream) {
-  B200_CHECK_ARG(qc && q_plain && q_full && cache && latent_norm_w && rot_freq && positions && slot_mapping &&
+  B200_CHECK_ARG(qc && q_plain && q_full && cache && latent_norm_w && (rot_dims == 0 || rot_freq) && positions && slot_mapping &&
                      heads > 0 && dim >= 0 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim &&
                      rot_dims % 2 == 0 && kv_rank > 0 && (dt == 0 || dt == 1),
                  "latent_prep: bad arguments");
@@ -571,16 +581,35 @@ void b200_latent_prep(const float* qc, int32_t ldq, void* q_plain, float* q_full
                            num_tokens, heads, dim, rot_dim, rot_dims, kv_rank, eps, dt,
                            reinterpret_cast<cudaStream_t>(stream));
 }
+void b200_latent_prep_queries(const float* qc, int32_t ldq, void* q_plain, float* q_full, const double* rot_freq,
+                              float rot_mag, const int64_t* positions, int32_t num_tokens, int32_t heads, int32_t dim,
+                              int32_t rot_dim, int32_t rot_dims, int32_t kv_rank, int32_t dt, int64_t stream) {
+  B200_CHECK_ARG(qc && q_plain && q_full && (rot_dims == 0 || rot_freq) && positions && heads > 0 && dim >= 0 &&
+                     rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0 && kv_rank > 0 &&
+                     (dt == 0 || dt == 1),
+                 "latent_prep_queries: bad arguments");
+  b200::launch_latent_prep(qc, ldq, q_plain, q_full, nullptr, nullptr, rot_freq, rot_mag, positions, nullptr, num_tokens,
+                           heads, dim, rot_dim, rot_dims, kv_rank, 0.f, dt, reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_latent_attn_gated(void* out, const float* q_full, const void* cache, const float* sink, const float* gate,
+                            int32_t ld_gate, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                            const uint32_t* block_tables, int32_t max_blocks_per_seq, int32_t num_seqs,
+                            int32_t num_tokens, int32_t heads, int32_t kv_rank, int32_t rot_dim, int32_t window,
+                            float scale, int32_t dt, void* workspace, int64_t stream) {
+  B200_CHECK_ARG(out && q_full && cache && cu_seqlens_q && context_lens && block_tables && num_seqs > 0 && heads > 0 &&
+                     kv_rank > 0 && rot_dim >= 0 && (dt == 0 || dt == 1),
+                 "latent_attn: bad arguments");
+  b200::launch_latent_attn(out, q_full, cache, sink, gate, ld_gate, cu_seqlens_q, context_lens, block_tables,
+                           max_blocks_per_seq, num_seqs, num_tokens, heads, kv_rank, rot_dim, window, scale, dt,
+                           workspace, reinterpret_cast<cudaStream_t>(stream));
+}
 void b200_latent_attn(void* out, const float* q_full, const void* cache, const float* sink,
                       const uint32_t* cu_seqlens_q, const uint32_t* context_lens, const uint32_t* block_tables,
                       int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens, int32_t heads, int32_t kv_rank,
                       int32_t rot_dim, int32_t window, float scale, int32_t dt, void* workspace, int64_t stream) {
-  B200_CHECK_ARG(out && q_full && cache && cu_seqlens_q && context_lens && block_tables && num_seqs > 0 && heads > 0 &&
-                     kv_rank > 0 && rot_dim >= 0 && (dt == 0 || dt == 1),
-                 "latent_attn: bad arguments");
-  b200::launch_latent_attn(out, q_full, cache, sink, cu_seqlens_q, context_lens, block_tables, max_blocks_per_seq,
-                           num_seqs, num_tokens, heads, kv_rank, rot_dim, window, scale, dt, workspace,
-                           reinterpret_cast<cudaStream_t>(stream));
+  b200_latent_attn_gated(out, q_full, cache, sink, nullptr, 0, cu_seqlens_q, context_lens, block_tables,
+                         max_blocks_per_seq, num_seqs, num_tokens, heads, kv_rank, rot_dim, window, scale, dt, workspace,
+                         stream);
 }
 int64_t b200_latent_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_rank, int32_t window) {
   return static_cast<int64_t>(b200::latent_attn_workspace_bytes(num_tokens, heads, kv_rank, window));

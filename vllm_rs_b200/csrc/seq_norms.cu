@@ -10,14 +10,27 @@
 namespace b200 {
 using namespace seqmix;
 
+// pos_base > 0: the sinusoidal position vector of the token's position p joins the row: entry 2i is
+// sin(p * base^(-2i / width)), entry 2i + 1 the cosine of the same angle (frequency, angle, sine and cosine in fp32)
 template <typename T>
 __global__ void embed_f32_kernel(float* __restrict__ x, const T* __restrict__ table, const uint32_t* __restrict__ ids,
-                                 int width, int vocab, float scale) {
+                                 const int64_t* __restrict__ positions, float pos_base, int width, int vocab,
+                                 float scale) {
   const int t = blockIdx.x;
   uint32_t id = ids[t];
   if (id >= static_cast<uint32_t>(vocab)) id = 0;
   const T* row = table + static_cast<size_t>(id) * width;
-  for (int d = threadIdx.x; d < width; d += blockDim.x) x[static_cast<size_t>(t) * width + d] = ld(row + d) * scale;
+  const bool with_pos = pos_base > 0.f && positions != nullptr;
+  const float p = with_pos ? static_cast<float>(positions[t]) : 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    float v = ld(row + d) * scale;
+    if (with_pos) {
+      const float freq = powf(pos_base, -static_cast<float>(d & ~1) / static_cast<float>(width));
+      const float ang = p * freq;
+      v += (d & 1) ? cosf(ang) : sinf(ang);
+    }
+    x[static_cast<size_t>(t) * width + d] = v;
+  }
 }
 
 // out[r] = x[row(r)] / sqrt(mean(x^2) + eps) * (w_offset + w); rows == nullptr: row(r) = r
@@ -101,18 +114,31 @@ __global__ void silu_mul_f32_kernel(T* __restrict__ out, const float* __restrict
   }
 }
 
+template <typename T>
+__global__ void relu2_f32_kernel(T* __restrict__ out, const float* __restrict__ up, int ld, int ff, int gate_col,
+                                 size_t total) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = i / ff, d = i % ff;
+    const float u = fmaxf(up[t * ld + d], 0.f);
+    const float g = gate_col >= 0 ? sigmoid_f(up[t * ld + gate_col]) : 1.f;
+    st(out + i, u * u * g);
+  }
+}
+
 static int flat_grid(size_t total) {
   const size_t b = (total + 255) / 256;
   return static_cast<int>(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
 }
 
-void launch_embed_f32(float* x, const void* table, const uint32_t* ids, int T, int width, int vocab, float scale, int dt,
-                      cudaStream_t st_) {
+void launch_embed_f32(float* x, const void* table, const uint32_t* ids, const int64_t* positions, float pos_base, int T,
+                      int width, int vocab, float scale, int dt, cudaStream_t st_) {
   if (T <= 0) return;
   if (dt)
-    embed_f32_kernel<float><<<T, 256, 0, st_>>>(x, (const float*)table, ids, width, vocab, scale);
+    embed_f32_kernel<float><<<T, 256, 0, st_>>>(x, (const float*)table, ids, positions, pos_base, width, vocab, scale);
   else
-    embed_f32_kernel<__nv_bfloat16><<<T, 256, 0, st_>>>(x, (const __nv_bfloat16*)table, ids, width, vocab, scale);
+    embed_f32_kernel<__nv_bfloat16><<<T, 256, 0, st_>>>(x, (const __nv_bfloat16*)table, ids, positions, pos_base, width,
+                                                        vocab, scale);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -172,6 +198,16 @@ void launch_silu_mul_f32(void* out, const float* gate_up, int T, int ff, int dt,
     silu_mul_f32_kernel<float><<<flat_grid(total), 256, 0, st_>>>((float*)out, gate_up, ff, total);
   else
     silu_mul_f32_kernel<__nv_bfloat16><<<flat_grid(total), 256, 0, st_>>>((__nv_bfloat16*)out, gate_up, ff, total);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_relu2_f32(void* out, const float* up, int ld, int T, int ff, int gate_col, int dt, cudaStream_t st_) {
+  const size_t total = static_cast<size_t>(T) * ff;
+  if (total == 0) return;
+  if (dt)
+    relu2_f32_kernel<float><<<flat_grid(total), 256, 0, st_>>>((float*)out, up, ld, ff, gate_col, total);
+  else
+    relu2_f32_kernel<__nv_bfloat16><<<flat_grid(total), 256, 0, st_>>>((__nv_bfloat16*)out, up, ld, ff, gate_col, total);
   B200_CUDA_LAUNCH_CHECK();
 }
 

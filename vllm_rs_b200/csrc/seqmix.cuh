@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../../include/b200_vllm.h"
 #include "common.cuh"
 
 namespace b200 {
@@ -69,8 +70,9 @@ __device__ __forceinline__ int seq_of_row(const uint32_t* __restrict__ cu, int n
 }  // namespace seqmix
 
 // ---- launchers (seq_norms.cu, latent_attn.cu, window_attn.cu, linear_recurrence.cu, moe.cu, gemm_lib.cu); dt: 0 bf16, 1 fp32
-void launch_embed_f32(float* x, const void* table, const uint32_t* ids, int T, int width, int vocab, float scale, int dt,
-                      cudaStream_t st);
+// positions / pos_base: pos_base > 0 adds the sinusoidal position vector (sin at even, cos at odd entries)
+void launch_embed_f32(float* x, const void* table, const uint32_t* ids, const int64_t* positions, float pos_base, int T,
+                      int width, int vocab, float scale, int dt, cudaStream_t st);
 void launch_resid_rmsnorm(void* out, const float* x, const float* w, int T, int width, float eps, float w_offset,
                           const uint32_t* rows, int dt, cudaStream_t st);
 void launch_gated_group_norm(void* out, const float* y, int ldy, const float* gate, int ldg, const float* w, int w_period,
@@ -80,24 +82,28 @@ void launch_resid_add_rmsnorm(float* x, const float* y, const float* w, int T, i
 void launch_bias_rows(float* y, const float* bias, float scale, int T, int n, cudaStream_t st);
 void launch_cast_rows(void* out, const float* in, int ld_in, int T, int n, int dt, cudaStream_t st);
 void launch_silu_mul_f32(void* out, const float* gate_up, int T, int ff, int dt, cudaStream_t st);
+// out [T, ff] = relu(up[t, d])^2 (* sigmoid(up[t, gate_col]) when gate_col >= 0); up fp32 with row stride ld
+void launch_relu2_f32(void* out, const float* up, int ld, int T, int ff, int gate_col, int dt, cudaStream_t st);
 
 void launch_latent_prep(const float* qc, int ldq, void* q_plain, float* q_full, void* cache, const float* latent_norm_w,
                         const double* rot_freq, float rot_mag, const int64_t* positions, const int64_t* slots, int T,
                         int heads, int dim, int rot_dim, int rot_dims, int kv_rank, float eps, int dt, cudaStream_t st);
-void launch_latent_attn(void* out, const float* q_full, const void* cache, const float* sink, const uint32_t* cu,
-                        const uint32_t* ctx, const uint32_t* block_tables, int max_blocks, int num_seqs, int T, int heads,
-                        int kv_rank, int rot_dim, int window, float scale, int dt, void* workspace, cudaStream_t st);
+// cache == nullptr: the row holds queries only (a layer that reads another layer's cache); gate: per-head output gate
+void launch_latent_attn(void* out, const float* q_full, const void* cache, const float* sink, const float* gate,
+                        int ld_gate, const uint32_t* cu, const uint32_t* ctx, const uint32_t* block_tables,
+                        int max_blocks, int num_seqs, int T, int heads, int kv_rank, int rot_dim, int window, float scale,
+                        int dt, void* workspace, cudaStream_t st);
 size_t latent_attn_workspace_bytes(int T, int heads, int kv_rank, int window);
 
 void launch_window_attn_prep(const float* proj, int ld, const float* bias, const float* q_norm_w, const float* k_norm_w,
                              const double* rot_freq, const int64_t* positions, const int64_t* slots, float* q_out,
                              void* k_cache, void* v_cache, int T, int heads, int kv_heads, int dim, int vdim,
-                             int rot_dims, float eps, int dt, cudaStream_t st);
+                             int rot_dims, float eps, int dt, const b200_attn_options* opt, cudaStream_t st);
 void launch_window_attn(void* out, const float* q, const void* k_cache, const void* v_cache, const float* sink,
                         const float* gate, int ld_gate, const uint32_t* cu, const uint32_t* ctx,
                         const uint32_t* block_tables, int max_blocks, int num_seqs, int T, int heads, int kv_heads,
                         int dim, int vdim, int window, int keep_first, float scale, float softcap, int dt,
-                        void* workspace, cudaStream_t st);
+                        void* workspace, const b200_attn_options* opt, cudaStream_t st);
 size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first);
 
 void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const float* taps_w, const float* bias,
@@ -119,16 +125,20 @@ void launch_decay_attn(float* out, const float* q, const float* k, const float* 
                        const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads, int dim,
                        int vdim, cudaStream_t st);
 
-void launch_moe_route(const float* logits, int T, int E, int top, float scale, int32_t* top_idx, float* top_w,
-                      cudaStream_t st);
+void launch_moe_route(const float* logits, const float* bias, int T, int E, int top, int groups, int keep, float scale,
+                      int32_t* top_idx, float* top_w, cudaStream_t st);
 void launch_moe_sort(const int32_t* top_idx, int pairs, int E, int32_t* expert_off, int32_t* pair_of_slot,
                      int32_t* slot_of_pair, cudaStream_t st);
-void launch_moe_gate_up(void* act, const void* h, const void* w_gate_up, const int32_t* expert_off,
-                        const int32_t* pair_of_slot, int pairs, int top, int E, int width, int ff, int dt, cudaStream_t st);
+// act 0: SiLU(gate) * up over [gate | up] rows; act 1: relu(up)^2 over up rows
+void launch_moe_gate_up(void* act_out, const void* h, const void* w_up, const int32_t* expert_off,
+                        const int32_t* pair_of_slot, int pairs, int top, int E, int width, int ff, int act, int dt,
+                        cudaStream_t st);
 void launch_moe_down(float* out, const void* act, const void* w_down, const int32_t* expert_off, int pairs, int E,
                      int width, int ff, int dt, cudaStream_t st);
-void launch_moe_combine(float* x, const float* down, const int32_t* slot_of_pair, const float* top_w, int T, int top,
-                        int width, cudaStream_t st);
+// x = (accumulate ? x : 0) + sum of the choices; choices >= E are identity experts and read `ident`
+void launch_moe_combine(float* x, const float* down, const int32_t* slot_of_pair, const int32_t* top_idx,
+                        const float* top_w, int T, int top, int width, int E, const void* ident, int ident_f32, int dt,
+                        int accumulate, cudaStream_t st);
 
 // C[M, N] (fp32, ldc) = beta * C + A[M, K] (lda) x W[N, K]^T (ldw); operands bf16 or fp32, fp32 accumulation, no
 // reduced-precision mode for fp32 operands.  `batch` > 1: strided batches.  w_kn != 0: W is stored [K, N] (ldw >= N).

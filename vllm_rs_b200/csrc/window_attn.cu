@@ -10,7 +10,13 @@
 //   * capped scores: s <- cap * tanh(s / cap)  (cap <= 0: off), applied after the scale
 //   * a per-head sink logit that joins the softmax denominator without a key or value (NULL: none); a logit of 0
 //     contributes exp(0) = 1, i.e. p_j = e^(s_j) / (1 + sum_k e^(s_k))
-//   * a per-head output gate: the head's output is multiplied by sigmoid(gate[t, h]) (NULL: none)
+//   * a per-head output gate: the head's output is multiplied by sigmoid(gate[t, h]) (NULL: none), or a gate per
+//     output element (gate[t, h * vdim + d])
+//   * a distance bias: slope_h * (i - j) is taken off the score of query position i and key position j (after scale
+//     and cap; slopes fp32 per head, NULL: none)
+//   * in the prep kernel: q / k norms per head with one weight of size dim shared by the heads (instead of over the
+//     whole projection), values that are the un-normed key rows (no v projection), and a query temperature
+//     1 + coef * ln(floor((p + 1) / every) + 1) at position p
 //
 // window_attn_prep_kernel: from the fused projection row [q (heads x dim) | k (kv_heads x dim) | v (kv_heads x vdim) | ...]
 // (fp32) it adds the projection biases, RMS-norms q and k over their WHOLE projection (all heads at once, weights of
@@ -36,21 +42,26 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
                                         const double* __restrict__ rot_freq, const int64_t* __restrict__ positions,
                                         const int64_t* __restrict__ slots, float* __restrict__ q_out,
                                         T* __restrict__ k_cache, T* __restrict__ v_cache, int heads, int kv_heads,
-                                        int dim, int vdim, int rot_dims, float eps) {
-  extern __shared__ float sm[];          // cos[rot_dims/2] | sin[rot_dims/2] | red[33]
+                                        int dim, int vdim, int rot_dims, float eps, int head_norm, int v_from_k,
+                                        int q_temp_every, float q_temp_coef) {
+  extern __shared__ float sm[];          // cos[rot_dims/2] | sin[rot_dims/2] | red[36] | hinv[heads + kv_heads]
   const int half = rot_dims / 2;
   float* cs = sm;
   float* sn = sm + half;
   float* red = sm + 2 * half;
+  float* hinv = red + 36;
   const int t = blockIdx.x;
   const int nq = heads * dim, nk = kv_heads * dim, nv = kv_heads * vdim;
   const float* qr = proj + static_cast<size_t>(t) * ld;
   const float* kr = qr + nq;
-  const float* vr = kr + nk;
+  const float* vr = v_from_k ? kr : kr + nk;            // values = the key rows as projected (vdim == dim)
   const float* bq = bias;
   const float* bk = bias ? bias + nq : nullptr;
-  const float* bv = bias ? bias + nq + nk : nullptr;
+  const float* bv = bias ? (v_from_k ? bk : bias + nq + nk) : nullptr;
   const double pos = static_cast<double>(positions[t]);
+  const float q_temp = q_temp_every > 0
+                           ? 1.f + q_temp_coef * logf(static_cast<float>((positions[t] + 1) / q_temp_every) + 1.f)
+                           : 1.f;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     double s, c;
     sincos(pos * rot_freq[i], &s, &c);
@@ -58,7 +69,21 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
     sn[i] = static_cast<float>(s);
   }
   float inv_q = 1.f, inv_k = 1.f;
-  if (q_norm_w) {
+  if (head_norm) {                       // every q and k head on its own: a warp per head
+    const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int hh = warp; hh < heads + kv_heads; hh += nw) {
+      const bool isq = hh < heads;
+      const float* src = isq ? qr + hh * dim : kr + (hh - heads) * dim;
+      const float* b = isq ? (bq ? bq + hh * dim : nullptr) : (bk ? bk + (hh - heads) * dim : nullptr);
+      float ss = 0.f;
+      for (int d = lane; d < dim; d += 32) {
+        const float v = src[d] + (b ? b[d] : 0.f);
+        ss += v * v;
+      }
+      ss = lanes_sum(ss);
+      if (lane == 0) hinv[hh] = (isq ? q_norm_w : k_norm_w) ? 1.f / sqrtf(ss / static_cast<float>(dim) + eps) : 1.f;
+    }
+  } else if (q_norm_w) {
     float ss = 0.f;
     for (int d = threadIdx.x; d < nq; d += blockDim.x) {
       const float v = qr[d] + (bq ? bq[d] : 0.f);
@@ -67,7 +92,7 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
     ss = block_sum(ss, red);
     inv_q = 1.f / sqrtf(ss / static_cast<float>(nq) + eps);
   }
-  if (k_norm_w) {
+  if (!head_norm && k_norm_w) {
     float ss = 0.f;
     for (int d = threadIdx.x; d < nk; d += blockDim.x) {
       const float v = kr[d] + (bk ? bk[d] : 0.f);
@@ -78,8 +103,11 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
   }
   __syncthreads();                       // the cos / sin table is complete
   // one (possibly rotated) entry of a projection whose heads are `dim` wide
-  auto entry = [&](const float* raw, const float* b, const float* w, float inv, int e) {
-    auto plain = [&](int i) { return (raw[i] + (b ? b[i] : 0.f)) * inv * (w ? w[i] : 1.f); };
+  auto entry = [&](const float* raw, const float* b, const float* w, float inv, int hbase, int e) {
+    auto plain = [&](int i) {
+      const float v = raw[i] + (b ? b[i] : 0.f);
+      return head_norm ? v * hinv[hbase + i / dim] * (w ? w[i % dim] : 1.f) : v * inv * (w ? w[i] : 1.f);
+    };
     const int d = e % dim;
     if (d >= rot_dims) return plain(e);
     const int i = d >> 1, e0 = e - (d & 1);
@@ -87,11 +115,11 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
     return (d & 1) ? v * cs[i] + u * sn[i] : u * cs[i] - v * sn[i];
   };
   for (int e = threadIdx.x; e < nq; e += blockDim.x)
-    q_out[static_cast<size_t>(t) * nq + e] = entry(qr, bq, q_norm_w, inv_q, e);
+    q_out[static_cast<size_t>(t) * nq + e] = entry(qr, bq, q_norm_w, inv_q, 0, e) * q_temp;
   const int64_t slot = slots[t];
   if (slot >= 0) {
     for (int e = threadIdx.x; e < nk; e += blockDim.x)
-      st(k_cache + static_cast<size_t>(slot) * nk + e, entry(kr, bk, k_norm_w, inv_k, e));
+      st(k_cache + static_cast<size_t>(slot) * nk + e, entry(kr, bk, k_norm_w, inv_k, heads, e));
     for (int e = threadIdx.x; e < nv; e += blockDim.x)
       st(v_cache + static_cast<size_t>(slot) * nv + e, vr[e] + (bv ? bv[e] : 0.f));
   }
@@ -120,7 +148,8 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
                                    const uint32_t* __restrict__ ctx, const uint32_t* __restrict__ block_tables,
                                    int max_blocks, int num_seqs, int heads, int kv_heads, int dim, int vdim, int window,
                                    int keep_first, float scale, float softcap, int key_tile, int nsplit,
-                                   float* __restrict__ part_o, float* __restrict__ part_ml) {
+                                   float* __restrict__ part_o, float* __restrict__ part_ml,
+                                   const float* __restrict__ slopes, int gate_elems) {
   extern __shared__ float sm[];
   const int Dp = dim | 1;                               // odd row pitch: a lane per key reads conflict-free
   const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,6 +183,7 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
       m = sink[h];
       l = 1.f;
     }
+    const float slope = (live && slopes) ? slopes[h] : 0.f;
     for (int i0 = first; i0 < last; i0 += key_tile) {
       const int nk = min(key_tile, last - i0);
       __syncthreads();
@@ -177,7 +207,7 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
           const float* kr = ks + k * Dp;
           const float* qw = qs + warp * dim;
           for (int d = 0; d < dim; ++d) acc += qw[d] * kr[d];
-          s = cap_score(acc * scale, softcap);
+          s = cap_score(acc * scale, softcap) - slope * static_cast<float>(pos - vis.key(i0 + k));
         }
         const float mt = lanes_max(s);
         const float mn = fmaxf(m, mt);
@@ -200,9 +230,10 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
     }
     if (live && nsplit == 1) {
       float inv = l > 0.f ? 1.f / l : 0.f;
-      if (gate) inv *= sigmoid_f(gate[static_cast<size_t>(t) * ld_gate + h]);
+      if (gate && !gate_elems) inv *= sigmoid_f(gate[static_cast<size_t>(t) * ld_gate + h]);
+      const float* ge = (gate && gate_elems) ? gate + static_cast<size_t>(t) * ld_gate + static_cast<size_t>(h) * vdim : nullptr;
       T* o = out + (static_cast<size_t>(t) * heads + h) * vdim;
-      for (int d = lane; d < vdim; d += 32) st(o + d, os[warp * vdim + d] * inv);
+      for (int d = lane; d < vdim; d += 32) st(o + d, os[warp * vdim + d] * inv * (ge ? sigmoid_f(ge[d]) : 1.f));
     } else if (live) {
       const size_t pi = (static_cast<size_t>(t) * heads + h) * nsplit + blockIdx.z;
       for (int d = lane; d < vdim; d += 32) part_o[pi * vdim + d] = os[warp * vdim + d];
@@ -218,7 +249,8 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
 template <typename T>
 __global__ void window_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, const float* __restrict__ sink,
-                                         const float* __restrict__ gate, int ld_gate, int heads, int vdim, int nsplit) {
+                                         const float* __restrict__ gate, int ld_gate, int heads, int vdim, int nsplit,
+                                         int gate_elems) {
   const size_t th = blockIdx.x;
   const int h = static_cast<int>(th % heads);
   const size_t t = th / heads;
@@ -228,29 +260,37 @@ __global__ void window_attn_merge_kernel(T* __restrict__ out, const float* __res
   float l = sink ? expf(sink[h] - m) : 0.f;
   for (int z = 0; z < nsplit; ++z) l += ml[2 * z + 1] * expf(ml[2 * z] - m);
   float inv = l > 0.f ? 1.f / l : 0.f;
-  if (gate) inv *= sigmoid_f(gate[t * ld_gate + h]);
+  if (gate && !gate_elems) inv *= sigmoid_f(gate[t * ld_gate + h]);
+  const float* ge = (gate && gate_elems) ? gate + t * ld_gate + static_cast<size_t>(h) * vdim : nullptr;
   for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
     float acc = 0.f;
     for (int z = 0; z < nsplit; ++z) acc += part_o[(th * nsplit + z) * vdim + d] * expf(ml[2 * z] - m);
-    st(out + th * vdim + d, acc * inv);
+    st(out + th * vdim + d, acc * inv * (ge ? sigmoid_f(ge[d]) : 1.f));
   }
 }
 
 void launch_window_attn_prep(const float* proj, int ld, const float* bias, const float* q_norm_w, const float* k_norm_w,
                              const double* rot_freq, const int64_t* positions, const int64_t* slots, float* q_out,
                              void* k_cache, void* v_cache, int T, int heads, int kv_heads, int dim, int vdim,
-                             int rot_dims, float eps, int dt, cudaStream_t st_) {
+                             int rot_dims, float eps, int dt, const b200_attn_options* opt, cudaStream_t st_) {
   if (T <= 0) return;
-  const size_t smem = (static_cast<size_t>(rot_dims) + 40) * 4;
+  const int head_norm = opt ? opt->head_norm : 0, v_from_k = opt ? opt->v_from_k : 0;
+  const int q_every = opt ? opt->q_temp_every : 0;
+  const float q_coef = opt ? opt->q_temp_coef : 0.f;
+  if (v_from_k && vdim != dim) {
+    set_error(1, "window_attn_prep: values taken from the key rows need vdim == dim");
+    return;
+  }
+  const size_t smem = (static_cast<size_t>(rot_dims) + 40 + heads + kv_heads) * 4;
   if (dt)
     window_attn_prep_kernel<float><<<T, 256, smem, st_>>>(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions, slots,
                                                           q_out, (float*)k_cache, (float*)v_cache, heads, kv_heads, dim,
-                                                          vdim, rot_dims, eps);
+                                                          vdim, rot_dims, eps, head_norm, v_from_k, q_every, q_coef);
   else
     window_attn_prep_kernel<__nv_bfloat16><<<T, 256, smem, st_>>>(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions,
                                                                   slots, q_out, (__nv_bfloat16*)k_cache,
                                                                   (__nv_bfloat16*)v_cache, heads, kv_heads, dim, vdim,
-                                                                  rot_dims, eps);
+                                                                  rot_dims, eps, head_norm, v_from_k, q_every, q_coef);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -285,7 +325,8 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
                        const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
                        const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_heads,
                        int dim, int vdim, int window, int keep_first, float scale, float softcap, int nsplit,
-                       float* __restrict__ part_o, float* __restrict__ part_ml) {
+                       float* __restrict__ part_o, float* __restrict__ part_ml, const float* __restrict__ slopes,
+                       int gate_elems) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int P = dim + 8, PV = vdim + 8;                   // row pitches in bf16 elements (16-byte multiples)
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [WKT][P]
@@ -328,13 +369,14 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
     const float v = r < nrows ? q[qrow * dim + d] : 0.f;
     Qs[r * P + d] = __float2bfloat16_rn(v);
   }
-  float m[2], l[2];
+  float m[2], l[2], slope[2];
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
     const int hh = HROWS ? min(h + g + rr * 8, heads - 1) : h;
     const bool with_sink = sink && nsplit == 1;            // split runs add the sink when the parts are merged
     m[rr] = with_sink ? sink[hh] : -1e30f;
     l[rr] = with_sink ? 1.f : 0.f;
+    slope[rr] = slopes ? slopes[hh] : 0.f;
   }
   float o[NT][4];
 #pragma unroll
@@ -411,7 +453,8 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
         for (int c = 0; c < 4; ++c) {
           const int kcol = ks * 16 + 2 * tq + (c & 1) + (c >> 1) * 8, j = j0 + kcol;
           const bool ok = HROWS ? (r < nrows && j < t_end) : (r < nrows && j <= rowp[rr] && (j >= lo || j < keep_first));
-          const float v = ok ? Ss[r * (WKT + 1) + kcol] : -1e30f;
+          const int jpos = HROWS ? vis.key(min(j, t_end - 1)) : j;         // the key's position
+          const float v = ok ? Ss[r * (WKT + 1) + kcol] - slope[rr] * static_cast<float>(rowp[rr] - jpos) : -1e30f;
           p[rr][ks * 4 + c] = v;
           mx[rr] = fmaxf(mx[rr], v);
         }
@@ -470,11 +513,13 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
     const size_t orow = trow * heads + hh;
     if (nsplit == 1) {
       float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
-      if (gate) inv *= sigmoid_f(gate[trow * ld_gate + hh]);
+      if (gate && !gate_elems) inv *= sigmoid_f(gate[trow * ld_gate + hh]);
+      const float* ge = (gate && gate_elems) ? gate + trow * ld_gate + static_cast<size_t>(hh) * vdim : nullptr;
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
         const int d = (warp * NT + n) * 8 + 2 * tq;
-        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+        const float g0 = ge ? sigmoid_f(ge[d]) : 1.f, g1 = ge ? sigmoid_f(ge[d + 1]) : 1.f;
+        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv * g0, o[n][rr * 2 + 1] * inv * g1);
         *reinterpret_cast<__nv_bfloat162*>(out + orow * vdim + d) = v;
       }
     } else {
@@ -509,7 +554,8 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
                         const float* __restrict__ sink, const float* __restrict__ gate, int ld_gate,
                         const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
                         const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_heads,
-                        int dim, int vdim, int window, int keep_first, float scale, float softcap) {
+                        int dim, int vdim, int window, int keep_first, float scale, float softcap,
+                        const float* __restrict__ slopes, int gate_elems) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int P = dim + 8, PV = vdim + 8;
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [WKT][P]
@@ -533,6 +579,7 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
     if (b < 0) return;
   }
   const int h = blockIdx.y, kvh = h / (heads / kv_heads);
+  const float slope = slopes ? slopes[h] : 0.f;
   const int pos0 = static_cast<int>(ctx[b]) - static_cast<int>(cu[b + 1] - cu[b]) + (row0 - static_cast<int>(cu[b]));
   const int pos_last = pos0 + nrows - 1;
   const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
@@ -616,7 +663,8 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
         for (int c = 0; c < 2; ++c) {
           const int j = j0 + n * 8 + 2 * tq + c;
           const bool ok = rowi[rr] < nrows && j <= rowp[rr] && (j >= lo || j < keep_first);
-          const float v = ok ? cap_score(sc[n][rr * 2 + c] * scale, softcap) : -1e30f;
+          const float v = ok ? cap_score(sc[n][rr * 2 + c] * scale, softcap) - slope * static_cast<float>(rowp[rr] - j)
+                             : -1e30f;
           sc[n][rr * 2 + c] = v;
           mx[rr] = fmaxf(mx[rr], v);
         }
@@ -672,11 +720,13 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
     if (rowi[rr] >= nrows) continue;
     const size_t trow = static_cast<size_t>(row0 + rowi[rr]);
     float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
-    if (gate) inv *= sigmoid_f(gate[trow * ld_gate + h]);
+    if (gate && !gate_elems) inv *= sigmoid_f(gate[trow * ld_gate + h]);
+    const float* ge = (gate && gate_elems) ? gate + trow * ld_gate + static_cast<size_t>(h) * vdim : nullptr;
 #pragma unroll
     for (int n = 0; n < NTV; ++n) {
       const int d = n * 8 + 2 * tq;
-      __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+      const float g0 = ge ? sigmoid_f(ge[d]) : 1.f, g1 = ge ? sigmoid_f(ge[d + 1]) : 1.f;
+      __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv * g0, o[n][rr * 2 + 1] * inv * g1);
       *reinterpret_cast<__nv_bfloat162*>(out + (trow * heads + h) * vdim + d) = v;
     }
   }
@@ -734,8 +784,10 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
                         const float* gate, int ld_gate, const uint32_t* cu, const uint32_t* ctx,
                         const uint32_t* block_tables, int max_blocks, int num_seqs, int T, int heads, int kv_heads,
                         int dim, int vdim, int window, int keep_first, float scale, float softcap, int dt,
-                        void* workspace, cudaStream_t st_) {
+                        void* workspace, const b200_attn_options* opt, cudaStream_t st_) {
   if (T <= 0) return;
+  const float* slopes = opt ? opt->dist_slopes : nullptr;
+  const int gate_elems = opt ? opt->gate_elems : 0;
   // bf16, steps of many rows, value sizes up to 128: the tensor-core form with 64 token rows per block
   if (!dt && window_mma_enabled() && T > 2 * sm_count() / 4 && window_rows_enabled() && dim % 16 == 0 && vdim % 16 == 0 &&
       vdim <= 128) {
@@ -748,7 +800,7 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
     kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,                          \
                                    (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,      \
                                    max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,    \
-                                   softcap);                                                                       \
+                                   softcap, slopes, gate_elems);                                                   \
   }
     bool done = smem <= 200 * 1024;
     if (done) switch (vdim / 8) {
@@ -784,7 +836,7 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
     kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,                          \
                                    (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,      \
                                    max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,    \
-                                   softcap, nsplit, part_o, part_ml);                                              \
+                                   softcap, nsplit, part_o, part_ml, slopes, gate_elems);                          \
   }
 #define B200_WMMA(NT)                 \
   if (hrows) B200_WMMA2(NT, true)     \
@@ -806,7 +858,7 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
       if (nsplit > 1) {
         const int th = vdim >= 256 ? 256 : (vdim >= 128 ? 128 : 64);
         window_attn_merge_kernel<__nv_bfloat16><<<T * heads, th, 0, st_>>>((__nv_bfloat16*)out, part_o, part_ml, sink,
-                                                                           gate, ld_gate, heads, vdim, nsplit);
+                                                                           gate, ld_gate, heads, vdim, nsplit, gate_elems);
         B200_CUDA_LAUNCH_CHECK();
       }
       return;
@@ -834,24 +886,24 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, nw * 32, smem, st_>>>((float*)out, q, (const float*)k_cache, (const float*)v_cache, sink, gate, ld_gate,
                                        cu, ctx, block_tables, max_blocks, num_seqs, heads, kv_heads, dim, vdim, window,
-                                       keep_first, scale, softcap, key_tile, nsplit, part_o, part_ml);
+                                       keep_first, scale, softcap, key_tile, nsplit, part_o, part_ml, slopes, gate_elems);
   } else {
     auto kern = window_attn_kernel<__nv_bfloat16>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, nw * 32, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,
                                        (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,
                                        max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,
-                                       softcap, key_tile, nsplit, part_o, part_ml);
+                                       softcap, key_tile, nsplit, part_o, part_ml, slopes, gate_elems);
   }
   B200_CUDA_LAUNCH_CHECK();
   if (nsplit > 1) {
     const int th = vdim >= 256 ? 256 : (vdim >= 128 ? 128 : 64);
     if (dt)
       window_attn_merge_kernel<float><<<T * heads, th, 0, st_>>>((float*)out, part_o, part_ml, sink, gate, ld_gate,
-                                                                 heads, vdim, nsplit);
+                                                                 heads, vdim, nsplit, gate_elems);
     else
       window_attn_merge_kernel<__nv_bfloat16><<<T * heads, th, 0, st_>>>((__nv_bfloat16*)out, part_o, part_ml, sink,
-                                                                         gate, ld_gate, heads, vdim, nsplit);
+                                                                         gate, ld_gate, heads, vdim, nsplit, gate_elems);
     B200_CUDA_LAUNCH_CHECK();
   }
 }
@@ -859,30 +911,48 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
 }  // namespace b200
 
 extern "C" {
-void b200_window_attn_prep(const float* proj, int32_t ld, const float* bias, const float* q_norm_w,
-                           const float* k_norm_w, const double* rot_freq, const int64_t* positions,
-                           const int64_t* slot_mapping, float* q_out, void* k_cache, void* v_cache, int32_t num_tokens,
-                           int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t rot_dims, float eps,
-                           int32_t dt, int64_t stream) {
+void b200_window_attn_prep_ex(const float* proj, int32_t ld, const float* bias, const float* q_norm_w,
+                              const float* k_norm_w, const double* rot_freq, const int64_t* positions,
+                              const int64_t* slot_mapping, float* q_out, void* k_cache, void* v_cache,
+                              int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
+                              int32_t rot_dims, float eps, int32_t dt, const b200_attn_options* opt, int64_t stream) {
   B200_CHECK_ARG(proj && positions && slot_mapping && q_out && k_cache && v_cache && heads > 0 && kv_heads > 0 &&
                      heads % kv_heads == 0 && dim > 0 && vdim > 0 && rot_dims >= 0 && rot_dims <= dim &&
                      rot_dims % 2 == 0 && (rot_dims == 0 || rot_freq) && (dt == 0 || dt == 1),
                  "window_attn_prep: bad arguments");
   b200::launch_window_attn_prep(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, q_out, k_cache,
-                                v_cache, num_tokens, heads, kv_heads, dim, vdim, rot_dims, eps, dt,
+                                v_cache, num_tokens, heads, kv_heads, dim, vdim, rot_dims, eps, dt, opt,
                                 reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_window_attn_prep(const float* proj, int32_t ld, const float* bias, const float* q_norm_w,
+                           const float* k_norm_w, const double* rot_freq, const int64_t* positions,
+                           const int64_t* slot_mapping, float* q_out, void* k_cache, void* v_cache, int32_t num_tokens,
+                           int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t rot_dims, float eps,
+                           int32_t dt, int64_t stream) {
+  b200_window_attn_prep_ex(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, q_out, k_cache, v_cache,
+                           num_tokens, heads, kv_heads, dim, vdim, rot_dims, eps, dt, nullptr, stream);
+}
+void b200_window_attn_ex(void* out, const float* q, const void* k_cache, const void* v_cache, const float* sink,
+                         const float* gate, int32_t ld_gate, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                         const uint32_t* block_tables, int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens,
+                         int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t window, int32_t keep_first,
+                         float scale, float softcap, int32_t dt, void* workspace, const b200_attn_options* opt,
+                         int64_t stream) {
+  B200_CHECK_ARG(out && q && k_cache && v_cache && cu_seqlens_q && context_lens && block_tables && num_seqs > 0 &&
+                     heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && (dt == 0 || dt == 1),
+                 "window_attn: bad arguments");
+  b200::launch_window_attn(out, q, k_cache, v_cache, sink, gate, ld_gate, cu_seqlens_q, context_lens, block_tables,
+                           max_blocks_per_seq, num_seqs, num_tokens, heads, kv_heads, dim, vdim, window, keep_first,
+                           scale, softcap, dt, workspace, opt, reinterpret_cast<cudaStream_t>(stream));
 }
 void b200_window_attn(void* out, const float* q, const void* k_cache, const void* v_cache, const float* sink,
                       const float* gate, int32_t ld_gate, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
                       const uint32_t* block_tables, int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens,
                       int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t window, int32_t keep_first,
                       float scale, float softcap, int32_t dt, void* workspace, int64_t stream) {
-  B200_CHECK_ARG(out && q && k_cache && v_cache && cu_seqlens_q && context_lens && block_tables && num_seqs > 0 &&
-                     heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && (dt == 0 || dt == 1),
-                 "window_attn: bad arguments");
-  b200::launch_window_attn(out, q, k_cache, v_cache, sink, gate, ld_gate, cu_seqlens_q, context_lens, block_tables,
-                           max_blocks_per_seq, num_seqs, num_tokens, heads, kv_heads, dim, vdim, window, keep_first,
-                           scale, softcap, dt, workspace, reinterpret_cast<cudaStream_t>(stream));
+  b200_window_attn_ex(out, q, k_cache, v_cache, sink, gate, ld_gate, cu_seqlens_q, context_lens, block_tables,
+                      max_blocks_per_seq, num_seqs, num_tokens, heads, kv_heads, dim, vdim, window, keep_first, scale,
+                      softcap, dt, workspace, nullptr, stream);
 }
 int64_t b200_window_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t vdim,
                                          int32_t window, int32_t keep_first) {

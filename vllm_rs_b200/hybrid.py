@@ -1,8 +1,8 @@
 """Runner of hybrid decoders with an fp32 residual stream over the C++ launch plan (b200_hybrid_*,
 csrc/host/hybrid_runner.cpp): the sibling of engine.ModelRunner for models whose layers choose between latent
 attention, windowed softmax attention, the gated delta rule, the SSD scan and decayed linear attention (one mixer, or
-two side by side), with a routed mixture of experts or a dense gated feed-forward, in a parallel or a sandwich
-(norm before and after each sublayer) layout.
+two side by side), with a routed mixture of experts or a dense gated feed-forward, in a parallel, a sandwich
+(norm before and after each sublayer) or a post-norm (norm on each sublayer's output only) layout.
 
 This module holds no model arithmetic.  It allocates what the C side borrows -- the paged latent caches, the
 paged K / V caches, the slot-indexed recurrent state pools, the workspace, pinned staging -- describes the layers to it, and moves a step's
@@ -20,7 +20,7 @@ from . import _lib
 from ._lib import HybridConfig, HybridLayer
 
 MIXER_LATENT_ATTN, MIXER_DELTA_RULE, MIXER_SSD, MIXER_WINDOW_ATTN, MIXER_DECAY_ATTN = 0, 1, 2, 3, 4
-LAYOUT_PARALLEL, LAYOUT_SANDWICH = 0, 1
+LAYOUT_PARALLEL, LAYOUT_SANDWICH, LAYOUT_POSTNORM = 0, 1, 2
 PAGE = 64
 
 
@@ -32,11 +32,12 @@ class LayerSpec:
     dims: dict
     tensors: dict = field(default_factory=dict)
     side: "LayerSpec | None" = None      # a second mixer beside the first (reads the same norm; outputs are summed)
+    cache_from: "int | None" = None      # latent attention: read layer cache_from's latent cache (no cache of its own)
 
 
 class HybridRunner:
     def __init__(self, *, width, vocab, layers: list[LayerSpec], embed, final_norm, lm_head, norm_eps,
-                 norm_weight_offset=0.0, embed_scale=1.0, dtype=torch.bfloat16, num_blocks, max_blocks_per_seq, max_seqs, max_tokens,
+                 norm_weight_offset=0.0, embed_scale=1.0, embed_pos_base=0.0, dtype=torch.bfloat16, num_blocks, max_blocks_per_seq, max_seqs, max_tokens,
                  num_state_slots, device="cuda", layer_trace=False):
         if dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("hybrid decoders run with bfloat16 or float32 operands")
@@ -46,7 +47,8 @@ class HybridRunner:
         self.cfg = HybridConfig(width=width, vocab=vocab, num_layers=len(layers), dt=int(dtype == torch.float32),
                                 block_size=PAGE, num_blocks=num_blocks, max_blocks_per_seq=max_blocks_per_seq,
                                 max_seqs=max_seqs, max_tokens=max_tokens, num_state_slots=num_state_slots,
-                                norm_eps=norm_eps, norm_weight_offset=norm_weight_offset, embed_scale=embed_scale)
+                                norm_eps=norm_eps, norm_weight_offset=norm_weight_offset, embed_scale=embed_scale,
+                                embed_pos_base=embed_pos_base)
         self._h = self._l.b200_hybrid_new(C.byref(self.cfg))
         _lib.check()
         self._keep = [embed, final_norm, lm_head]
@@ -56,7 +58,16 @@ class HybridRunner:
         def describe(key, spec):
             """The C description of one mixer; allocates the caches / state pools it needs under `key`."""
             d, t = spec.dims, dict(spec.tensors)
-            if spec.mixer == MIXER_LATENT_ATTN:
+            if spec.mixer == MIXER_LATENT_ATTN and spec.cache_from is not None:
+                src = spec.cache_from
+                if not (isinstance(key, int) and 0 <= src < key and layers[src].mixer == MIXER_LATENT_ATTN and
+                        layers[src].cache_from is None and
+                        layers[src].dims["kv_rank"] + layers[src].dims["rot_dim"] == d["kv_rank"] + d["rot_dim"]):
+                    raise ValueError(f"layer {key}: a shared latent cache comes from an earlier latent-attention layer "
+                                     "of the same row size that writes its own")
+                t["kv_cache"] = self.kv_cache[src]
+                d = {**d, "shared_cache": 1}
+            elif spec.mixer == MIXER_LATENT_ATTN:
                 self.kv_cache[key] = torch.zeros(num_blocks, PAGE, d["kv_rank"] + d["rot_dim"], dtype=dtype,
                                                  device=self.device)
                 t["kv_cache"] = self.kv_cache[key]

@@ -6,6 +6,8 @@ sm_100a kernels from libb200_vllm.so; there is no CPU or eager-torch fallback.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from . import _lib
@@ -355,18 +357,32 @@ def latent_prep(qc, cache, latent_norm_w, rot_freq, rot_mag, positions, slot_map
     return q_plain, q_full
 
 
+def latent_prep_queries(q, rot_freq, rot_mag, positions, *, heads, dim, rot_dim, rot_dims, kv_rank, dtype):
+    """latent_prep for a layer that reads another layer's cache: q fp32 [T, heads (dim + rot_dim)] holds queries only."""
+    _cuda(q, rot_freq, positions)
+    T = q.shape[0]
+    q_plain = torch.empty(T, heads, dim, dtype=dtype, device=q.device)
+    q_full = torch.zeros(T, heads, kv_rank + rot_dim, dtype=torch.float32, device=q.device)
+    _lib.lib().b200_latent_prep_queries(_p(q), q.shape[1], _p(q_plain), _p(q_full), _p(rot_freq), float(rot_mag),
+                                        _p(positions), T, heads, dim, rot_dim, rot_dims, kv_rank, _dt(dtype), _stream())
+    _lib.check()
+    return q_plain, q_full
+
+
 def latent_attn(q_full, cache, sink, cu_seqlens_q, context_lens, block_tables, *, kv_rank, rot_dim, window, scale,
-                split=True):
+                split=True, gate=None):
     """Attention-weighted latents [T, heads, kv_rank] in the cache dtype.  split: give the kernel the workspace that
-    lets steps of few rows spread a row's keys over several blocks."""
-    _cuda(q_full, cache, sink, cu_seqlens_q, context_lens, block_tables)
+    lets steps of few rows spread a row's keys over several blocks.  gate fp32 [T, heads] logits or None: head h's
+    result is multiplied by sigmoid(gate[t, h])."""
+    _cuda(q_full, cache, sink, cu_seqlens_q, context_lens, block_tables, gate)
     T, H, _ = q_full.shape
     out = torch.empty(T, H, kv_rank, dtype=cache.dtype, device=q_full.device)
     nbytes = _lib.lib().b200_latent_attn_workspace_bytes(T, H, kv_rank, int(window)) if split else 0
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q_full.device) if nbytes else None
-    _lib.lib().b200_latent_attn(_p(out), _p(q_full), _p(cache), _p(sink), _p(cu_seqlens_q), _p(context_lens),
-                                _p(block_tables), block_tables.shape[1], context_lens.shape[0], T, H, kv_rank, rot_dim,
-                                int(window), float(scale), _dt(cache.dtype), _p(ws), _stream())
+    _lib.lib().b200_latent_attn_gated(_p(out), _p(q_full), _p(cache), _p(sink), _p(gate),
+                                      gate.shape[1] if gate is not None else 0, _p(cu_seqlens_q), _p(context_lens),
+                                      _p(block_tables), block_tables.shape[1], context_lens.shape[0], T, H, kv_rank,
+                                      rot_dim, int(window), float(scale), _dt(cache.dtype), _p(ws), _stream())
     _lib.check()
     return out
 
@@ -439,6 +455,36 @@ def moe_experts(x, h, top_idx, top_w, w_gate_up, w_down):
     return x
 
 
+def moe_route_ex(logits, bias, top, scale=1.0, groups=0, keep=0):
+    """Router with a selection bias (fp32 [E] or None) and groups: see b200_moe_route_ex."""
+    _cuda(logits, bias)
+    T, E = logits.shape
+    idx = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    _lib.lib().b200_moe_route_ex(_p(logits), _p(bias), T, E, int(top), int(groups), int(keep), float(scale), _p(idx),
+                                 _p(w), _stream())
+    _lib.check()
+    return idx, w
+
+
+def moe_experts_ex(out, h, top_idx, top_w, w_up, w_down, *, act="silu_gate", identity=0, accumulate=True, ident=None):
+    """out fp32 [T, D] (+)= the chosen experts of h [T, D]; act "silu_gate": w_up [E, 2 F, D]; "relu2": w_up [E, F, D];
+    indices >= E are identity experts and return the rows of `ident` (fp32 or h's dtype; default h)."""
+    ident = h if ident is None else ident
+    _cuda(out, h, top_idx, top_w, w_up, w_down, ident)
+    T, D = out.shape
+    E, rows, _ = w_up.shape
+    F = rows // 2 if act == "silu_gate" else rows
+    top = top_idx.shape[1]
+    nbytes = _lib.lib().b200_moe_workspace_bytes(T, E + identity, top, D, F)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=out.device)
+    _lib.lib().b200_moe_experts_ex(_p(out), _p(h), _p(top_idx), _p(top_w), _p(w_up), _p(w_down), T, E, int(identity), top,
+                                   D, F, {"silu_gate": 0, "relu2": 1}[act], int(bool(accumulate)), _p(ident),
+                                   int(ident.dtype == torch.float32), _dt(h.dtype), _p(ws), _stream())
+    _lib.check()
+    return out
+
+
 def resid_add_rmsnorm(x, y, w, eps, w_offset=0.0):
     """x fp32 [T, D] += y / rms(y) * (w_offset + w), in place."""
     _cuda(x, y, w)
@@ -447,35 +493,49 @@ def resid_add_rmsnorm(x, y, w, eps, w_offset=0.0):
     return x
 
 
+def _attn_options(head_norm=False, v_from_k=False, q_temp=None, dist_slopes=None, gate_elems=False):
+    """b200_attn_options; q_temp = (coef, every) or None.  Keep the returned object alive during the call."""
+    o = _lib.AttnOptions(head_norm=int(bool(head_norm)), v_from_k=int(bool(v_from_k)),
+                         q_temp_every=int(q_temp[1]) if q_temp else 0, gate_elems=int(bool(gate_elems)),
+                         q_temp_coef=float(q_temp[0]) if q_temp else 0.0,
+                         dist_slopes=dist_slopes.data_ptr() if dist_slopes is not None else None)
+    return o
+
+
 def window_attn_prep(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, k_cache, v_cache, *, heads,
-                     rot_dims, eps):
+                     rot_dims, eps, head_norm=False, v_from_k=False, q_temp=None):
     """proj fp32 [T, >= heads dim + kv_heads (dim + vdim)] -> q fp32 [T, heads, dim]; writes the K / V cache rows
-    (k_cache [blocks, 64, kv_heads, dim], v_cache [blocks, 64, kv_heads, vdim])."""
+    (k_cache [blocks, 64, kv_heads, dim], v_cache [blocks, 64, kv_heads, vdim]).  head_norm: q_norm_w / k_norm_w are
+    [dim] and every head is normed on its own; v_from_k: no v block, values = the key rows as projected; q_temp =
+    (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1)."""
     _cuda(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, k_cache, v_cache)
     T = proj.shape[0]
     G, dk, dv = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
     q = torch.empty(T, heads, dk, dtype=torch.float32, device=proj.device)
-    _lib.lib().b200_window_attn_prep(_p(proj), proj.shape[1], _p(bias), _p(q_norm_w), _p(k_norm_w), _p(rot_freq),
-                                     _p(positions), _p(slot_mapping), _p(q), _p(k_cache), _p(v_cache), T, heads, G, dk,
-                                     dv, int(rot_dims), float(eps), _dt(k_cache.dtype), _stream())
+    opt = _attn_options(head_norm, v_from_k, q_temp)
+    _lib.lib().b200_window_attn_prep_ex(_p(proj), proj.shape[1], _p(bias), _p(q_norm_w), _p(k_norm_w), _p(rot_freq),
+                                        _p(positions), _p(slot_mapping), _p(q), _p(k_cache), _p(v_cache), T, heads, G, dk,
+                                        dv, int(rot_dims), float(eps), _dt(k_cache.dtype), C.byref(opt), _stream())
     _lib.check()
     return q
 
 
 def window_attn(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables, *, window, keep_first, scale,
-                softcap=0.0, split=True):
-    """q fp32 [T, heads, dim] -> [T, heads, vdim] in the cache dtype; gate fp32 [T, heads] logits or None."""
-    _cuda(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables)
+                softcap=0.0, split=True, dist_slopes=None):
+    """q fp32 [T, heads, dim] -> [T, heads, vdim] in the cache dtype; gate fp32 logits [T, heads] (one per head) or
+    [T, heads vdim] (one per output element) or None; dist_slopes fp32 [heads]: slope (i - j) is taken off the scores."""
+    _cuda(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables, dist_slopes)
     T, H, dk = q.shape
     G, dv = k_cache.shape[2], v_cache.shape[3]
     out = torch.empty(T, H, dv, dtype=k_cache.dtype, device=q.device)
     nbytes = _lib.lib().b200_window_attn_workspace_bytes(T, H, G, dv, int(window), int(keep_first)) if split else 0
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
-    _lib.lib().b200_window_attn(_p(out), _p(q), _p(k_cache), _p(v_cache), _p(sink), _p(gate),
-                                gate.shape[1] if gate is not None else 0, _p(cu_seqlens_q), _p(context_lens),
-                                _p(block_tables), block_tables.shape[1], context_lens.shape[0], T, H, G, dk, dv,
-                                int(window), int(keep_first), float(scale), float(softcap), _dt(k_cache.dtype), _p(ws),
-                                _stream())
+    opt = _attn_options(dist_slopes=dist_slopes, gate_elems=gate is not None and gate.shape[1] == H * dv and dv > 1)
+    _lib.lib().b200_window_attn_ex(_p(out), _p(q), _p(k_cache), _p(v_cache), _p(sink), _p(gate),
+                                   gate.shape[1] if gate is not None else 0, _p(cu_seqlens_q), _p(context_lens),
+                                   _p(block_tables), block_tables.shape[1], context_lens.shape[0], T, H, G, dk, dv,
+                                   int(window), int(keep_first), float(scale), float(softcap), _dt(k_cache.dtype), _p(ws),
+                                   C.byref(opt), _stream())
     _lib.check()
     return out
 
