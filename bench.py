@@ -21,6 +21,12 @@ Configs (BASELINE.json `configs`):
                       linear attention layers, dense feed-forward, a norm before and after every sublayer; fp32 residual,
                       bf16 operands, random weights) next to the Fidasun decoder of equal width and depth: prefill and
                       decode tokens/s of both and the kernels of both timed alone (vllm_rs_b200/bench_zalalix.py).
+  gibevik             the Gibevik decoder (post-norm layers; grouped-head attention with a distance bias, values taken
+                      from the keys and an element gate; gated latent attention with caches shared between layers; dense
+                      and routed squared-ReLU feed-forwards with expert groups and identity experts; fp32 residual, bf16
+                      operands, random weights) next to the Fidasun decoder of equal width and depth: prefill and decode
+                      tokens/s of both, and each kernel alone with and without its new options
+                      (vllm_rs_b200/bench_gibevik.py).
 
 Keys of the JSON line:
   value  device-resident: step inputs already in HBM, K CUDA-graph replays of the SAME step (the same KV slot is
@@ -59,6 +65,7 @@ CONFIGS = {
                     label="Qwen2-72B GPTQ-int4"),
     "fidasun": dict(model="fidasun", fmt="bf16", kind="hybrid", baseline=None, label="Fidasun hybrid decoder"),
     "zalalix": dict(model="zalalix", fmt="bf16", kind="hybrid", baseline=None, label="Zalalix decoder"),
+    "gibevik": dict(model="gibevik", fmt="bf16", kind="hybrid", baseline=None, label="Gibevik decoder"),
     "l70_tp8": dict(model="llama3-70b", fmt="awq", kind="serve", gpus=8, max_num_seqs=64, requests=96,
                     prompt=(512, 2048), max_tokens=64, mean_gap_steps=1.0, baseline="configs[4]",
                     label="Llama-3-70B AWQ-int4"),
@@ -82,7 +89,7 @@ def parse():
     ap.add_argument("--no-extra-configs", action="store_true", help="N = 4 / 8: skip the q72_tp4 / l70_tp8 legs")
     ap.add_argument("--py-step", action="store_true",
                     help="e2e: drive the step from Python over the individual C symbols instead of b200_engine_step")
-    ap.add_argument("--size", default="w2048,w4096", help="--config fidasun / zalalix: layer sizes, comma separated")
+    ap.add_argument("--size", default="w2048,w4096", help="--config fidasun / zalalix / gibevik: layer sizes, comma separated")
     ap.add_argument("--dense-arm", action="store_true",
                     help="--config fidasun: also time the dense fp16 plan of equal size now (time-limited process)")
     ap.add_argument("--prefill-tokens", type=int, default=8192,
@@ -764,10 +771,13 @@ def run_b200(args):
     elif c["kind"] == "hybrid":
         if cx.world != 1:
             raise SystemExit(f"--config {cfgname} is a single-GPU configuration")
-        from vllm_rs_b200 import _lib, bench_hybrid, bench_zalalix
+        from vllm_rs_b200 import _lib, bench_gibevik, bench_hybrid, bench_zalalix
         launches0 = _lib.lib().b200_launch_count()
         with ClockSampler(cx.local) as clk:
-            if cfgname == "zalalix":
+            if cfgname == "gibevik":
+                sizes = [bench_gibevik.run(sz, layers=args.layers or 4, prefill=4096, batch=args.batch, ctx=2048,
+                                           reps=max(args.steps // 4, 3)) for sz in args.size.split(",")]
+            elif cfgname == "zalalix":
                 sizes = [bench_zalalix.run(sz, layers=args.layers or 4, prefill=4096, batch=args.batch, ctx=2048,
                                            reps=max(args.steps // 4, 3)) for sz in args.size.split(",")]
             else:

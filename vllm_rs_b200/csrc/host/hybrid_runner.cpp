@@ -537,7 +537,11 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long launches0 = launch_count();
-  launch_embed_f32(r->x, r->embed, input_ids, positions, c.embed_pos_base, T, c.width, c.vocab, c.embed_scale, c.dt, st);
+  // post-norm layers read the stream itself: in bf16 runs the kernel that last wrote x also leaves its rounding in h
+  const bool first_reads_stream = r->layers[0].layout == B200_LAYOUT_POSTNORM && !c.dt;
+  launch_embed_f32(r->x, r->embed, input_ids, positions, c.embed_pos_base, T, c.width, c.vocab, c.embed_scale, c.dt,
+                   first_reads_stream ? r->h : nullptr, st);
+  bool h_is_x = first_reads_stream;          // h holds the bf16 rounding of the current x
   for (int i = 0; i < c.num_layers; ++i) {
     const b200_hybrid_layer& l = r->layers[i];
     const b200_hybrid_layer& side = r->sides[i];
@@ -546,27 +550,31 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
       // the sublayers read the stream itself: rounded to bf16 for the products, in place for fp32 runs
       auto stream_in = [&]() {
         if (c.dt) r->hin = r->x;
-        else launch_cast_rows(r->h, r->x, c.width, T, c.width, 0, st);
+        else if (!h_is_x) launch_cast_rows(r->h, r->x, c.width, T, c.width, 0, st);
       };
+      void* cast = c.dt ? nullptr : r->h;
       stream_in();
       run_mixer(r, l, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->y, l.out_scale,
                 0.f, st);
       if (side.heads > 0)
         run_mixer(r, side, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->y,
                   side.out_scale, 1.f, st);
-      launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.post_norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, st);
+      launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.post_norm_w, T, c.width, c.norm_eps, c.norm_weight_offset,
+                               cast, st);
+      h_is_x = cast != nullptr;
       if (l.experts > 0 || l.shared_ff > 0) {
         stream_in();
         if (l.experts > 0) feed_forward(r, l, T, r->y, false, r->x, 1, st);
         else dense_ffn(r, l, T, st);
         launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.ff_post_norm_w, T, c.width, c.norm_eps,
-                                 c.norm_weight_offset, st);
+                                 c.norm_weight_offset, cast, st);
       }
       if (r->trace)
         cudaMemcpyAsync(r->trace + static_cast<size_t>(i) * c.max_tokens * c.width, r->x,
                         static_cast<size_t>(T) * c.width * 4, cudaMemcpyDeviceToDevice, st);
       continue;
     }
+    h_is_x = false;
     launch_resid_rmsnorm(r->h, r->x, (const float*)l.norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, nullptr,
                          c.dt, st);
     if (l.layout == B200_LAYOUT_SANDWICH) {
@@ -575,13 +583,14 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
       if (side.heads > 0)
         run_mixer(r, side, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->y,
                   side.out_scale, 1.f, st);
-      launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.post_norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, st);
+      launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.post_norm_w, T, c.width, c.norm_eps, c.norm_weight_offset,
+                               nullptr, st);
       if (l.shared_ff > 0) {
         launch_resid_rmsnorm(r->h, r->x, (const float*)l.ff_norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, nullptr,
                              c.dt, st);
         dense_ffn(r, l, T, st);
         launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.ff_post_norm_w, T, c.width, c.norm_eps,
-                                 c.norm_weight_offset, st);
+                                 c.norm_weight_offset, nullptr, st);
       }
     } else {
       run_mixer(r, l, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->x, l.out_scale,

@@ -15,7 +15,7 @@ using namespace seqmix;
 template <typename T>
 __global__ void embed_f32_kernel(float* __restrict__ x, const T* __restrict__ table, const uint32_t* __restrict__ ids,
                                  const int64_t* __restrict__ positions, float pos_base, int width, int vocab,
-                                 float scale) {
+                                 float scale, T* __restrict__ cast_out) {
   const int t = blockIdx.x;
   uint32_t id = ids[t];
   if (id >= static_cast<uint32_t>(vocab)) id = 0;
@@ -30,6 +30,7 @@ __global__ void embed_f32_kernel(float* __restrict__ x, const T* __restrict__ ta
       v += (d & 1) ? cosf(ang) : sinf(ang);
     }
     x[static_cast<size_t>(t) * width + d] = v;
+    if (cast_out) st(cast_out + static_cast<size_t>(t) * width + d, v);     // the row as the first sublayer reads it
   }
 }
 
@@ -75,9 +76,10 @@ __global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __rest
 }
 
 
-// x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * (w_offset + w): the norm AFTER a sublayer, folded into the residual sum
+// x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * (w_offset + w): the norm AFTER a sublayer, folded into the residual sum.
+// cast_out (may be NULL): the new row rounded to bf16, for a next sublayer that reads the stream itself.
 __global__ void resid_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w,
-                                         int width, float eps, float w_offset) {
+                                         int width, float eps, float w_offset, __nv_bfloat16* __restrict__ cast_out) {
   __shared__ float red[33];
   const int t = blockIdx.x;
   const float* yr = y + static_cast<size_t>(t) * width;
@@ -85,8 +87,12 @@ __global__ void resid_add_rmsnorm_kernel(float* __restrict__ x, const float* __r
   for (int d = threadIdx.x; d < width; d += blockDim.x) ss += yr[d] * yr[d];
   ss = block_sum(ss, red);
   const float inv = 1.f / sqrtf(ss / static_cast<float>(width) + eps);
-  for (int d = threadIdx.x; d < width; d += blockDim.x)
-    x[static_cast<size_t>(t) * width + d] += yr[d] * inv * (w_offset + w[d]);
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const size_t i = static_cast<size_t>(t) * width + d;
+    const float v = x[i] + yr[d] * inv * (w_offset + w[d]);
+    x[i] = v;
+    if (cast_out) cast_out[i] = __float2bfloat16_rn(v);
+  }
 }
 
 // y[t, d] += scale * bias[d]
@@ -132,13 +138,14 @@ static int flat_grid(size_t total) {
 }
 
 void launch_embed_f32(float* x, const void* table, const uint32_t* ids, const int64_t* positions, float pos_base, int T,
-                      int width, int vocab, float scale, int dt, cudaStream_t st_) {
+                      int width, int vocab, float scale, int dt, void* cast_out, cudaStream_t st_) {
   if (T <= 0) return;
   if (dt)
-    embed_f32_kernel<float><<<T, 256, 0, st_>>>(x, (const float*)table, ids, positions, pos_base, width, vocab, scale);
+    embed_f32_kernel<float><<<T, 256, 0, st_>>>(x, (const float*)table, ids, positions, pos_base, width, vocab, scale,
+                                                nullptr);
   else
     embed_f32_kernel<__nv_bfloat16><<<T, 256, 0, st_>>>(x, (const __nv_bfloat16*)table, ids, positions, pos_base, width,
-                                                        vocab, scale);
+                                                        vocab, scale, (__nv_bfloat16*)cast_out);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -168,9 +175,9 @@ void launch_gated_group_norm(void* out, const float* y, int ldy, const float* ga
 }
 
 void launch_resid_add_rmsnorm(float* x, const float* y, const float* w, int T, int width, float eps, float w_offset,
-                              cudaStream_t st_) {
+                              void* cast_out, cudaStream_t st_) {
   if (T <= 0) return;
-  resid_add_rmsnorm_kernel<<<T, 256, 0, st_>>>(x, y, w, width, eps, w_offset);
+  resid_add_rmsnorm_kernel<<<T, 256, 0, st_>>>(x, y, w, width, eps, w_offset, (__nv_bfloat16*)cast_out);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -238,6 +245,7 @@ void b200_gated_group_norm(void* out, const float* y, int32_t ldy, const float* 
 void b200_resid_add_rmsnorm(float* x, const float* y, const float* w, int32_t num_tokens, int32_t width, float eps,
                             float w_offset, int64_t stream) {
   B200_CHECK_ARG(x && y && w && width > 0, "resid_add_rmsnorm: bad arguments");
-  b200::launch_resid_add_rmsnorm(x, y, w, num_tokens, width, eps, w_offset, reinterpret_cast<cudaStream_t>(stream));
+  b200::launch_resid_add_rmsnorm(x, y, w, num_tokens, width, eps, w_offset, nullptr,
+                                 reinterpret_cast<cudaStream_t>(stream));
 }
 }

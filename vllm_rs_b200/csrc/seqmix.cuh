@@ -70,15 +70,17 @@ __device__ __forceinline__ int seq_of_row(const uint32_t* __restrict__ cu, int n
 }  // namespace seqmix
 
 // ---- launchers (seq_norms.cu, latent_attn.cu, window_attn.cu, linear_recurrence.cu, moe.cu, gemm_lib.cu); dt: 0 bf16, 1 fp32
-// positions / pos_base: pos_base > 0 adds the sinusoidal position vector (sin at even, cos at odd entries)
+// positions / pos_base: pos_base > 0 adds the sinusoidal position vector (sin at even, cos at odd entries); cast_out
+// (bf16 runs, may be NULL): the rows rounded to bf16 as well
 void launch_embed_f32(float* x, const void* table, const uint32_t* ids, const int64_t* positions, float pos_base, int T,
-                      int width, int vocab, float scale, int dt, cudaStream_t st);
+                      int width, int vocab, float scale, int dt, void* cast_out, cudaStream_t st);
 void launch_resid_rmsnorm(void* out, const float* x, const float* w, int T, int width, float eps, float w_offset,
                           const uint32_t* rows, int dt, cudaStream_t st);
 void launch_gated_group_norm(void* out, const float* y, int ldy, const float* gate, int ldg, const float* w, int w_period,
                              int T, int C, int group, float eps, int gate_first, int gate_act, int dt, cudaStream_t st);
+// cast_out (may be NULL): the updated rows rounded to bf16 as well
 void launch_resid_add_rmsnorm(float* x, const float* y, const float* w, int T, int width, float eps, float w_offset,
-                              cudaStream_t st);
+                              void* cast_out, cudaStream_t st);
 void launch_bias_rows(float* y, const float* bias, float scale, int T, int n, cudaStream_t st);
 void launch_cast_rows(void* out, const float* in, int ld_in, int T, int n, int dt, cudaStream_t st);
 void launch_silu_mul_f32(void* out, const float* gate_up, int T, int ff, int dt, cudaStream_t st);
