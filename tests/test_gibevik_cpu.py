@@ -16,6 +16,12 @@ def test_registry_knows_the_family():
     assert models.architecture_of({"architecture": "Gibevik"}) == "Gibevik"
 
 
+def test_command_line_lists_the_architecture(capsys):
+    from vllm_rs_b200.__main__ import main
+    assert main(["models"]) == 0
+    assert "Gibevik" in capsys.readouterr().out.split()
+
+
 @pytest.mark.parametrize("heads", [1, 3, 8, 12])
 def test_head_slopes(heads):
     from vllm_rs_b200.models.gibevik import head_slopes

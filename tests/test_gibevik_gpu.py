@@ -480,3 +480,66 @@ def test_random_configurations_under_random_schedules(lib, seed, dtype):
     if dtype == torch.float32:
         for k in reqs:
             assert rel_err(d.result(k), want[k]) <= tol, k
+
+
+# ------------------------------------------------------------------ a model folder through the command line
+def _write_model_folder(path, cfg, tensors):
+    """config.json and model.safetensors (8-byte little-endian header length, JSON header, raw data), bf16 tensors."""
+    import json
+    import struct
+    header, blobs, at = {}, [], 0
+    for name, t in tensors.items():
+        raw = t.contiguous().view(torch.uint8).numpy().tobytes() if t.dtype != torch.bfloat16 else \
+            t.contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    with open(path / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+    with open(path / "config.json", "w") as f:
+        json.dump(cfg, f)
+
+
+def test_model_folder_through_trace_runner_and_generate(lib, tmp_path):
+    """The registry picks the model by config.json; the trace runner replays two interleaved requests on a pool of
+    three pages (the second request reuses the first one's page and slot), `generate` decodes greedily."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cfg = full_cfg()
+    w = random_tensors(cfg, seed=23)
+    assert all(t.dtype == torch.bfloat16 for t in w.values())
+    _write_model_folder(tmp_path, cfg, w)
+    V = cfg["vocab"]
+    a, b, c = toks(70, V, 1), toks(9, V, 2), toks(64, V, 3)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": [0, 39]}, {"id": "b", "tokens": b[:2], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[2:], "want": [6]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[40:69], "want": [28]}, {"id": "c", "tokens": c, "want": [63]}], "end": ["c"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[69:], "want": [0]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps), text=True,
+                       capture_output=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.split("\n") if ln.startswith("done")] == [f"done {i}" for i in range(4)]
+    ra, rb, rc = ref_logits(cfg, w, a), ref_logits(cfg, w, b), ref_logits(cfg, w, c)
+    want = {0: ra[[0, 39]], 1: rb[[8]], 2: np.stack([ra[68], rc[63]]), 3: ra[[69]]}
+    for i, ref in want.items():
+        got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+        assert rel_err(got, ref) <= 2 * F32_TOL, i
+    r = subprocess.run([sys.executable, "-m", "vllm_rs_b200", "generate", "--model", str(tmp_path), "--dtype", "float32",
+                        "--prompt-ids", ",".join(map(str, b)), "--max-new-tokens", "5"], cwd=root, text=True,
+                       capture_output=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = json.loads(r.stdout.strip().split("\n")[-1])["output_ids"]
+    seq = list(b)
+    for k in range(5):
+        lg = ref_logits(cfg, w, seq)[-1]
+        top2 = np.sort(lg)[-2:]
+        if top2[1] - top2[0] < 1e-3:
+            break
+        assert got[k] == int(lg.argmax()), k
+        seq.append(int(lg.argmax()))
