@@ -682,8 +682,8 @@ void b200_runner_set_tp_fused(b200_runner*, int32_t on);
  * outputs are summed, each times its out_scale.                                                                   */
 #define B200_LAYOUT_PARALLEL 0
 #define B200_LAYOUT_SANDWICH 1
-/* POSTNORM: a norm on each sublayer's OUTPUT only: x += post_norm(mixer(x)), then x += ff_post_norm(ff(x)); the
- * sublayers read the stream itself (rounded to the operand dtype).  The feed-forward is the routed experts (with their
+/* POSTNORM: every sublayer's result is normed before it joins the stream and nothing is normed on the way in:
+ * x += post_norm(mixer(x)), then x += ff_post_norm(ff(x)), the inputs being x rounded to the operand dtype.  The feed-forward is the routed experts (with their
  * shared expert) when experts > 0, else the dense gated feed-forward (shared_ff), as in SANDWICH.                  */
 #define B200_LAYOUT_POSTNORM 2
 
@@ -719,11 +719,11 @@ int64_t b200_window_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int3
                                          int32_t window, int32_t keep_first);
 /* Further options of the two calls above (a zeroed struct = the plain calls).
  *   head_norm   != 0: q_norm_w / k_norm_w are fp32 [dim], shared by all heads, and every head is RMS-normed on its own
- *   v_from_k    != 0: the projection row has no v block; the value row is the key row as projected (bias added, before
+ *   v_from_k    != 0: the projection row has no v block; the value row is a copy of the raw key row (bias added, before
  *                     the key norm and rotation), so vdim == dim
  *   q_temp_coef, q_temp_every: every > 0: the query at position p is multiplied by
  *                     1 + coef * ln(floor((p + 1) / every) + 1)                       (after norm and rotation)
- *   dist_slopes fp32 [heads] or NULL: slope_h * (i - j) is taken off the score of query position i and key position j
+ *   dist_slopes fp32 [heads] or NULL: the score of query position i against key position j is lowered by slope_h * (i - j)
  *                     (after scale and cap)
  *   gate_elems  != 0: the output gate has heads x vdim logits per token (one per output element) instead of heads   */
 typedef struct b200_attn_options {

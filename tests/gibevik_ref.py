@@ -54,7 +54,7 @@ def biased_attention(h, w, p, m, eps):
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
     q = (h @ w[p + "q"].T).reshape(n, H, D)
     k = (h @ w[p + "k"].T).reshape(n, G, D)
-    v = k                                               # as projected, before the key norm
+    v = k                                               # the raw rows: the key norm below does not touch them
     qn = norm(q, w[p + "q.norm"], eps)
     kn = norm(k, w[p + "k.norm"], eps)
     qt = m.get("q_temp")

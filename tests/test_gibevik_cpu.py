@@ -35,7 +35,7 @@ def test_head_slopes(heads):
 def test_config_reader_rejects_what_the_design_excludes():
     from vllm_rs_b200.models import build_runner
     kw = dict(dtype=torch.float32, device="cpu", num_blocks=2, max_blocks_per_seq=2, max_seqs=1, max_tokens=64)
-    bad = make_cfg([layer("attention", None, dim=16, vdim=8)])        # values are the keys: vdim must equal dim
+    bad = make_cfg([layer("attention", None, dim=16, vdim=8)])        # raw key rows serve as values: vdim must equal dim
     with pytest.raises(ValueError):
         build_runner(bad, random_tensors(make_cfg([layer("attention", None)])), **kw)
     later = make_cfg([layer("latent_attention", None, kv_from=1), layer("latent_attention", None)])

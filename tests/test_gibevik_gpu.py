@@ -152,7 +152,7 @@ def test_attention_op_bias_gate_and_edges(lib, dtype, split, dk, H, G):
 
 
 def test_attention_prep_op(lib):
-    """Per-head norms with one shared weight, values = the keys as projected, and the query temperature at the places
+    """Per-head norms with one shared weight, raw key rows as values, and the query temperature at the places
     where its floor steps (position = every - 2, every - 1, 2 every - 1), against the plain formulas."""
     from vllm_rs_b200 import ops
     g = torch.Generator().manual_seed(3)
@@ -257,8 +257,8 @@ def test_layers_that_share_a_latent_cache(lib):
 # ------------------------------------------------------------------ router and experts
 def test_router_op_bias_groups_and_negative_scores(lib):
     """The router alone: choice by softmax + bias inside the kept groups only, weights without the bias.  With a bias of
-    -5 everywhere every choice score is negative: members of dropped groups must still not win (they count as minus
-    infinity, not as zero).  A bias that lifts one group's best member decides which groups stay."""
+    -5 everywhere every choice score is negative: members of dropped groups must still not win (a dropped member must
+    not be treated as a score of zero).  A bias that lifts one group's best member decides which groups stay."""
     from vllm_rs_b200 import ops
     g = torch.Generator().manual_seed(5)
     T, E = 50, 12

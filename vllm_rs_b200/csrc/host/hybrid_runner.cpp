@@ -24,8 +24,8 @@
 // Sandwich layer (a norm before AND after each sublayer): the mixers of the layer (one, or two side by side with their
 // scales) write their sum into y, then x += post_norm(y) (resid_add_rmsnorm); the dense gated feed-forward reads
 // ff_norm(x), writes y, and x += ff_post_norm(y).
-// Post-norm layer (a norm on each sublayer's output only): the sublayers read the stream itself, rounded to the operand
-// dtype (cast_rows; fp32 runs read x in place): y = mixers(x), x += post_norm(y); y = ff(x), x += ff_post_norm(y), the
+// Post-norm layer (results are normed on their way into the stream, inputs are not): the sublayers take x rounded to the
+// operand dtype (cast_rows; fp32 runs read x in place): y = mixers(x), x += post_norm(y); y = ff(x), x += ff_post_norm(y), the
 // feed-forward being the routed experts (plus their shared expert) or the dense gated one.
 #include <cuda_runtime.h>
 
@@ -537,7 +537,7 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long launches0 = launch_count();
-  // post-norm layers read the stream itself: in bf16 runs the kernel that last wrote x also leaves its rounding in h
+  // the sublayers of post-norm layers take the un-normed stream: in bf16 runs the kernel that last wrote x also leaves its rounding in h
   const bool first_reads_stream = r->layers[0].layout == B200_LAYOUT_POSTNORM && !c.dt;
   launch_embed_f32(r->x, r->embed, input_ids, positions, c.embed_pos_base, T, c.width, c.vocab, c.embed_scale, c.dt,
                    first_reads_stream ? r->h : nullptr, st);
@@ -547,7 +547,7 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
     const b200_hybrid_layer& side = r->sides[i];
     r->hin = r->h;
     if (l.layout == B200_LAYOUT_POSTNORM) {
-      // the sublayers read the stream itself: rounded to bf16 for the products, in place for fp32 runs
+      // sublayer input = x: rounded to bf16 for the products, in place for fp32 runs
       auto stream_in = [&]() {
         if (c.dt) r->hin = r->x;
         else if (!h_is_x) launch_cast_rows(r->h, r->x, c.width, T, c.width, 0, st);

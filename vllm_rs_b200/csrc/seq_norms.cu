@@ -77,7 +77,7 @@ __global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __rest
 
 
 // x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * (w_offset + w): the norm AFTER a sublayer, folded into the residual sum.
-// cast_out (may be NULL): the new row rounded to bf16, for a next sublayer that reads the stream itself.
+// cast_out (may be NULL): the new row rounded to bf16, for a next sublayer whose input is the un-normed stream.
 __global__ void resid_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w,
                                          int width, float eps, float w_offset, __nv_bfloat16* __restrict__ cast_out) {
   __shared__ float red[33];

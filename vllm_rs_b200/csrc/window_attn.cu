@@ -12,8 +12,8 @@
 //     contributes exp(0) = 1, i.e. p_j = e^(s_j) / (1 + sum_k e^(s_k))
 //   * a per-head output gate: the head's output is multiplied by sigmoid(gate[t, h]) (NULL: none), or a gate per
 //     output element (gate[t, h * vdim + d])
-//   * a distance bias: slope_h * (i - j) is taken off the score of query position i and key position j (after scale
-//     and cap; slopes fp32 per head, NULL: none)
+//   * a distance bias: the score of query position i against key position j is lowered by slope_h * (i - j), after
+//     scale and cap (slopes fp32 per head, NULL: none)
 //   * in the prep kernel: q / k norms per head with one weight of size dim shared by the heads (instead of over the
 //     whole projection), values that are the un-normed key rows (no v projection), and a query temperature
 //     1 + coef * ln(floor((p + 1) / every) + 1) at position p
@@ -54,7 +54,7 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
   const int nq = heads * dim, nk = kv_heads * dim, nv = kv_heads * vdim;
   const float* qr = proj + static_cast<size_t>(t) * ld;
   const float* kr = qr + nq;
-  const float* vr = v_from_k ? kr : kr + nk;            // values = the key rows as projected (vdim == dim)
+  const float* vr = v_from_k ? kr : kr + nk;            // the value row is a copy of the raw key row (vdim == dim)
   const float* bq = bias;
   const float* bk = bias ? bias + nq : nullptr;
   const float* bv = bias ? (v_from_k ? bk : bias + nq + nk) : nullptr;

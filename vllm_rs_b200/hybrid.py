@@ -2,7 +2,7 @@
 csrc/host/hybrid_runner.cpp): the sibling of engine.ModelRunner for models whose layers choose between latent
 attention, windowed softmax attention, the gated delta rule, the SSD scan and decayed linear attention (one mixer, or
 two side by side), with a routed mixture of experts or a dense gated feed-forward, in a parallel, a sandwich
-(norm before and after each sublayer) or a post-norm (norm on each sublayer's output only) layout.
+(norm before and after each sublayer) or a post-norm (sublayer results normed on their way into the stream) layout.
 
 This module holds no model arithmetic.  It allocates what the C side borrows -- the paged latent caches, the
 paged K / V caches, the slot-indexed recurrent state pools, the workspace, pinned staging -- describes the layers to it, and moves a step's

@@ -3,8 +3,8 @@
 config.json: {"architecture": "Gibevik", "width", "vocab", "norm": {"eps"}, "layers": [{"type", "mixer": {...},
 "mlp": {...} | null}, ...]}; tensors are named "embed", "l<i>.norm1", "l<i>.norm2", "l<i>.mix.*", "l<i>.mlp.*",
 "final.norm", "head", linear weights [out, in].  A sinusoidal position vector joins the embedding row, and every layer
-is post-norm: x += norm1(mixer(x)), then x += norm2(ff(x)); the sublayers read the stream itself.  Mixer types:
-  attention        : softmax attention with grouped key / value heads whose values ARE the keys as projected (no value
+is post-norm: x += norm1(mixer(x)), then x += norm2(ff(x)), with x going into the sublayers un-normed.  Mixer types:
+  attention        : softmax attention with grouped key heads whose raw, un-normed rows double as the values (no value
                      projection), RMS norm per q / k head with one weight shared by the heads, no rotation, a query
                      temperature that grows with the logarithm of the position, a linear distance bias with one fixed
                      slope per head, and an output gate per element
@@ -58,7 +58,7 @@ def build(cfg, tensors, *, dtype=torch.bfloat16, device="cuda", num_blocks, max_
             mixer = MIXER_WINDOW_ATTN
             H, G, dk, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
             if dv != dk:
-                raise ValueError(f"layer {i}: the values are the keys, so vdim must equal dim")
+                raise ValueError(f"layer {i}: the raw key rows serve as values, so vdim must equal dim")
             qt = m.get("q_temp") or {}
             d.update(heads=H, kv_heads=G, dim=dk, vdim=dv, scale=float(m["scale"]), gated=2, head_norm=1, v_from_k=1,
                      q_temp_every=int(qt.get("every", 0)), q_temp_coef=float(qt.get("coef", 0.0)))

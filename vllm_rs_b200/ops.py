@@ -506,7 +506,7 @@ def window_attn_prep(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_m
                      rot_dims, eps, head_norm=False, v_from_k=False, q_temp=None):
     """proj fp32 [T, >= heads dim + kv_heads (dim + vdim)] -> q fp32 [T, heads, dim]; writes the K / V cache rows
     (k_cache [blocks, 64, kv_heads, dim], v_cache [blocks, 64, kv_heads, vdim]).  head_norm: q_norm_w / k_norm_w are
-    [dim] and every head is normed on its own; v_from_k: no v block, values = the key rows as projected; q_temp =
+    [dim] and every head is normed on its own; v_from_k: no v block, the raw key rows are the values; q_temp =
     (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1)."""
     _cuda(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, k_cache, v_cache)
     T = proj.shape[0]
@@ -523,7 +523,7 @@ def window_attn_prep(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_m
 def window_attn(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables, *, window, keep_first, scale,
                 softcap=0.0, split=True, dist_slopes=None):
     """q fp32 [T, heads, dim] -> [T, heads, vdim] in the cache dtype; gate fp32 logits [T, heads] (one per head) or
-    [T, heads vdim] (one per output element) or None; dist_slopes fp32 [heads]: slope (i - j) is taken off the scores."""
+    [T, heads vdim] (one per output element) or None; dist_slopes fp32 [heads]: scores are lowered by slope (i - j)."""
     _cuda(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables, dist_slopes)
     T, H, dk = q.shape
     G, dv = k_cache.shape[2], v_cache.shape[3]
