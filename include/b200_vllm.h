@@ -686,6 +686,15 @@ void b200_runner_set_tp_fused(b200_runner*, int32_t on);
  * x += post_norm(mixer(x)), then x += ff_post_norm(ff(x)), the inputs being x rounded to the operand dtype.  The feed-forward is the routed experts (with their
  * shared expert) when experts > 0, else the dense gated feed-forward (shared_ff), as in SANDWICH.                  */
 #define B200_LAYOUT_POSTNORM 2
+/* PRENORM: the sublayers follow one another, each behind its own norm of the stream and each added to it times a
+ * factor: x += out_scale * mixer(norm(x)), then x += ff_scale * ff(ff_norm(x)).  The feed-forward is chosen as in
+ * POSTNORM.  The mixer's input may pass a token shift first (shift_w), and the layer may close with an average over
+ * the results of all layers so far (depth_w); both are described at b200_hybrid_layer.                              */
+#define B200_LAYOUT_PRENORM 3
+/* Norm kinds of the stream norms (norm_kind of a layer, final_norm_kind of the model).  RMS: x / sqrt(mean(x^2) + eps)
+ * * (offset + w).  DYNTANH: tanh(alpha * x) * w + b, element by element, no mean or variance (eps is not used).   */
+#define B200_NORM_RMS 0
+#define B200_NORM_DYNTANH 1
 
 void b200_resid_rmsnorm(void* out, const float* x, const float* w, int32_t num_tokens, int32_t width, float eps,
                         float w_offset, int32_t dt, int64_t stream);
@@ -696,6 +705,19 @@ void b200_gated_group_norm(void* out, const float* y, int32_t ldy, const float* 
 /* x fp32 [T, width] += y / sqrt(mean(y^2) + eps) * (w_offset + w): the norm after a sublayer and its residual sum */
 void b200_resid_add_rmsnorm(float* x, const float* y, const float* w, int32_t num_tokens, int32_t width, float eps,
                             float w_offset, int64_t stream);
+/* A norm of the stream with an optional token shift behind it.  n[t] = norm(x[t]) (kind B200_NORM_*; bias may be NULL);
+ * with shift_w (fp32 [width]): out[t] = n[t] + (n[t-1] - n[t]) * shift_w, n[t-1] being the un-shifted norm of the
+ * sequence's previous token: the row before in this step, or shift_state[slot] (fp32 [slots, width]) for the first row
+ * of a portion, or zeros at position 0.  The un-shifted norm of a sequence's last row becomes its shift_state.  out has
+ * dtype dt.  rows (u32, may be NULL; not with a shift): the stream rows to norm, out row r = norm(x[rows[r]]).       */
+void b200_stream_norm(void* out, const float* x, const float* w, const float* bias, float alpha, int32_t kind,
+                      float eps, float w_offset, const uint32_t* rows, const float* shift_w, float* shift_state,
+                      const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                      int32_t num_seqs, int32_t num_tokens, int32_t width, int32_t dt, int64_t stream);
+/* out fp32 [n] = sum over j < count of w[j] * hist[j * stride + i]: a weighted sum of `count` stored streams (w fp32
+ * [count], on the device).  out may be one of the streams' successors but none of the `count` inputs.              */
+void b200_depth_mix(float* out, const float* hist, int64_t stride, const float* w, int32_t count, int64_t n,
+                    int64_t stream);
 /* Windowed softmax attention with grouped K / V heads (csrc/window_attn.cu).  proj fp32 [T, ld] = [q: heads x dim |
  * k: kv_heads x dim | v: kv_heads x vdim | ...]; bias fp32 over q | k | v or NULL; q_norm_w / k_norm_w fp32 over the WHOLE
  * q / k projection or NULL (no norm); the first rot_dims entries of every q and k head are rotated as interleaved
@@ -730,7 +752,31 @@ typedef struct b200_attn_options {
   int32_t head_norm, v_from_k, q_temp_every, gate_elems;
   float q_temp_coef;
   const float* dist_slopes;
+  /* (fields below: zero = off)
+   *   rot_half    != 0: rotary pairs are (i, i + rot_dims / 2) (the two halves of the rotated part) instead of (2i, 2i+1)
+   *   rot_mag     != 0: cos and sin of the q / k rotation are multiplied by it (0 reads as 1)
+   *   v_rot_freq  f64 [vdim / 2] or NULL: the value row of position j is rotated by j * v_rot_freq[m] over all of vdim
+   *                     (same pair layout as rot_half says) before it is cached; b200_attn_finish turns a head's output
+   *                     back by its own position
+   *   v_heads     > 0: the value cache has v_heads heads and key head g reads value head g % v_heads (several score
+   *                     maps over one set of values: the maps' key heads are laid out map after map); 0: kv_heads
+   *   chunk       > 0: position i sees j <= i only if floor(i / chunk) == floor(j / chunk) (chunks count from position 0)
+   *   out_f32     != 0: the attention writes fp32 whatever dt says (for b200_attn_finish)
+   *   no_cache    != 0 (prep): the projection row holds queries only, nothing is written to a cache                  */
+  int32_t rot_half;
+  float rot_mag;
+  const double* v_rot_freq;
+  int32_t v_heads, chunk, out_f32, no_cache;
 } b200_attn_options;
+/* What follows the softmax-weighted sums where more than a gate does: out [T, heads, vdim] (dtype dt) from a fp32
+ * [T, maps * heads, vdim] (map after map).  maps == 2: o = a[map 0] - lambda * a[map 1] (differential attention).
+ * v_rot_freq (f64 [vdim / 2], or NULL): o is turned back by -position * v_rot_freq[m] (pairs as rot_half says).
+ * head_norm != 0: o / sqrt(mean(o^2) + eps) over the head's vdim values, no weight.  Then o * out_scale, then the gate:
+ * sigmoid(gate[t, h]) per head or, gate_elems != 0, sigmoid(gate[t, h * vdim + d]) per element (gate NULL: none).  */
+void b200_attn_finish(void* out, const float* a, const float* gate, int32_t ld_gate, int32_t gate_elems,
+                      const int64_t* positions, const double* v_rot_freq, int32_t rot_half, int32_t maps, float lambda,
+                      int32_t head_norm, float eps, float out_scale, int32_t num_tokens, int32_t heads, int32_t vdim,
+                      int32_t dt, int64_t stream);
 void b200_window_attn_prep_ex(const float* proj, int32_t ld, const float* bias, const float* q_norm_w,
                               const float* k_norm_w, const double* rot_freq, const int64_t* positions,
                               const int64_t* slot_mapping, float* q_out, void* k_cache, void* v_cache,
@@ -746,6 +792,11 @@ void b200_window_attn_ex(void* out, const float* q, const void* k_cache, const v
  * [channels, rank], bias fp32 [channels] or NULL.                                                                  */
 void b200_lowrank_decay(float* out, const float* low, int32_t ld_low, const float* w2, const float* bias, float tau,
                         int32_t num_tokens, int32_t channels, int32_t rank, int64_t stream);
+/* kind 0: as b200_lowrank_decay.  kind 1: out = exp(-exp(a_log[c / a_period]) * softplus(bias + low w2^T)), the decay
+ * of a gated delta rule per key channel (a_log fp32 [channels / a_period]; tau is not used).                        */
+void b200_lowrank_decay_ex(float* out, const float* low, int32_t ld_low, const float* w2, const float* bias, float tau,
+                           int32_t kind, const float* a_log, int32_t a_period, int32_t num_tokens, int32_t channels,
+                           int32_t rank, int64_t stream);
 /* Linear attention with a decayed state: S <- diag(a_t) S + (k_scale k_t) v_t^T, o_t = S^T (q_scale q_t).  q, k fp32
  * [T, heads, dim], v [T, heads, vdim] (row stride ld); exactly one of head_decay fp32 [heads] (a constant per head)
  * and chan_decay fp32 [T, heads, dim] (row stride ld_decay); act != 0: SiLU on q, k and v first; out fp32
@@ -794,6 +845,12 @@ void b200_delta_rule(float* out, const float* q, const float* k, const float* v,
                      const float* a_raw, int32_t ld_ba, const float* a_log, const float* dt_bias, float* state,
                      const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
                      int32_t num_seqs, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int64_t stream);
+/* b200_delta_rule with one decay per head AND key channel: chan_decay fp32 [T, heads, dim] (row stride ld_decay) holds
+ * the decays themselves (b200_lowrank_decay_ex kind 1), row i of S is multiplied by chan_decay[t, h, i].           */
+void b200_delta_rule_chan(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* b_raw,
+                          int32_t ld_b, const float* chan_decay, int32_t ld_decay, float* state,
+                          const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                          int32_t num_seqs, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int64_t stream);
 /* x [T, heads, vdim], Bm / Cm [T, groups, nstate] (row stride ld), dt_raw [T, heads] (row stride ld_dt), fp32;
  * out fp32 [T, heads, vdim]; state fp32 [slots, heads, nstate, vdim]; d_skip may be NULL.                          */
 void b200_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm, int32_t ld, const float* dt_raw,
@@ -835,6 +892,7 @@ typedef struct b200_hybrid_config {
   float embed_scale;                        /* the embedding row is multiplied by it */
   float embed_pos_base;                     /* > 0: a sinusoidal position vector joins the embedding row: entry 2i is
                                                sin(p base^(-2i / width)), entry 2i + 1 the cosine of the same angle */
+  int32_t final_norm_kind;                  /* B200_NORM_*; DYNTANH: see b200_hybrid_set_final_norm */
 } b200_hybrid_config;
 
 typedef struct b200_hybrid_layer {
@@ -892,6 +950,31 @@ typedef struct b200_hybrid_layer {
   int32_t shared_gated;                     /* != 0: one more row closes w_shared_gate_up; the shared expert's output is
                                                multiplied by the sigmoid of that row's product with the token */
   const void* route_bias;                   /* fp32 [experts + identity_experts] or NULL */
+  /* ---- PRENORM layers, dynamic-tanh norms, token shift, depth average, rotated values, chunked and differential
+   * attention, the delta rule with a decay per key channel, dense feed-forwards with biases */
+  int32_t norm_kind;                        /* B200_NORM_* of norm_w (and ff_norm_w) */
+  float norm_alpha, ff_norm_alpha;          /* DYNTANH: the scalar inside the tanh */
+  const void *norm_b, *ff_norm_b;           /* DYNTANH: fp32 [width] bias (NULL: none) */
+  const void* shift_w;                      /* fp32 [width] or NULL: token shift of the mixer's input (b200_stream_norm) */
+  void* shift_state;                        /* fp32 [slots, width], caller-owned */
+  const void* depth_w;                      /* fp32 [layer + 2] or NULL: the layer's result X_(layer+1) is kept, and what
+                                               goes on is sum_j depth_w[j] X_j, X_0 being the embedding output */
+  float ff_scale;                           /* PRENORM: the feed-forward's output is multiplied by it */
+  const void *ff_up_bias, *ff_down_bias;    /* fp32 [shared_ff], [width] or NULL: biases of a squared-ReLU dense feed-forward */
+  /* window attention (see b200_attn_options).  score_maps == 2: differential attention; w_in holds
+   * [q: maps x heads x dim | k: maps x kv_heads x dim | v: kv_heads x vdim | gate], the maps one after the other, the
+   * K cache has maps x kv_heads heads, the V cache kv_heads; out = (a_0 - diff_lambda a_1), RMS-normed per head without a
+   * weight where diff_norm != 0, times diff_out_scale.  shared_cache != 0: w_in holds [q | gate] only and kv_cache /
+   * v_cache are an earlier layer's, which this layer only reads.                                                      */
+  int32_t rot_half, chunk, score_maps, diff_norm;
+  float diff_lambda, diff_out_scale;
+  const double* v_rot_freq;                 /* f64 [vdim / 2], device, or NULL */
+  /* delta rule: chan_rank > 0: one decay per head and key channel from a low-rank projection, w_in =
+   * [q | k | v | b: heads | low_a: chan_rank | low_g: gate_rank], decay = exp(-exp(a_log[h]) softplus(w_decay2 low_a +
+   * dt_bias)) with w_decay2 fp32 [heads x dim, chan_rank], dt_bias fp32 [heads x dim]; gate_rank > 0: the output gate's
+   * logits are w_gate2 low_g (w_gate2 fp32 [heads x vdim, gate_rank]) and the gate is a sigmoid (gate_act 1)          */
+  int32_t chan_rank, gate_rank;
+  const void* w_gate2;
 } b200_hybrid_layer;
 
 typedef struct b200_hybrid b200_hybrid;
@@ -903,6 +986,8 @@ void b200_hybrid_set_layer(b200_hybrid*, int32_t layer, const b200_hybrid_layer*
 void b200_hybrid_set_layer_side(b200_hybrid*, int32_t layer, const b200_hybrid_layer* side);
 /* embed [vocab, width], lm_head [vocab, width] in dtype dt; final_norm fp32 [width] */
 void b200_hybrid_set_globals(b200_hybrid*, const void* embed, const void* final_norm, const void* lm_head);
+/* final norm of kind DYNTANH: bias fp32 [width] (may be NULL) and the scalar inside the tanh */
+void b200_hybrid_set_final_norm(b200_hybrid*, const void* bias, float alpha);
 int64_t b200_hybrid_workspace_bytes(const b200_hybrid*);
 void b200_hybrid_set_workspace(b200_hybrid*, void* workspace, int64_t bytes);
 /* fp32 [num_layers, max_tokens, width] device buffer that receives the residual stream after every layer (NULL: off) */

@@ -51,14 +51,16 @@ class HybridConfig(C.Structure):
 
     _fields_ = [(n, c_i32) for n in ("width", "vocab", "num_layers", "dt", "block_size", "num_blocks",
                                      "max_blocks_per_seq", "max_seqs", "max_tokens", "num_state_slots")] + \
-               [("norm_eps", c_f32), ("norm_weight_offset", c_f32), ("embed_scale", c_f32), ("embed_pos_base", c_f32)]
+               [("norm_eps", c_f32), ("norm_weight_offset", c_f32), ("embed_scale", c_f32), ("embed_pos_base", c_f32),
+                ("final_norm_kind", c_i32)]
 
 
 class AttnOptions(C.Structure):
     """b200_attn_options (include/b200_vllm.h)."""
 
     _fields_ = [(n, c_i32) for n in ("head_norm", "v_from_k", "q_temp_every", "gate_elems")] + \
-               [("q_temp_coef", c_f32), ("dist_slopes", c_vp)]
+               [("q_temp_coef", c_f32), ("dist_slopes", c_vp), ("rot_half", c_i32), ("rot_mag", c_f32),
+                ("v_rot_freq", c_vp)] + [(n, c_i32) for n in ("v_heads", "chunk", "out_f32", "no_cache")]
 
 
 class HybridLayer(C.Structure):
@@ -80,7 +82,13 @@ class HybridLayer(C.Structure):
                [("head_norm", c_i32), ("v_from_k", c_i32), ("q_temp_every", c_i32), ("q_temp_coef", c_f32),
                 ("dist_slopes", c_vp)] + \
                [(n, c_i32) for n in ("shared_cache", "expert_act", "shared_act", "identity_experts", "route_groups",
-                                     "route_keep", "shared_gated")] + [("route_bias", c_vp)]
+                                     "route_keep", "shared_gated")] + [("route_bias", c_vp)] + \
+               [("norm_kind", c_i32), ("norm_alpha", c_f32), ("ff_norm_alpha", c_f32)] + \
+               [(n, c_vp) for n in ("norm_b", "ff_norm_b", "shift_w", "shift_state", "depth_w")] + \
+               [("ff_scale", c_f32), ("ff_up_bias", c_vp), ("ff_down_bias", c_vp)] + \
+               [(n, c_i32) for n in ("rot_half", "chunk", "score_maps", "diff_norm")] + \
+               [("diff_lambda", c_f32), ("diff_out_scale", c_f32), ("v_rot_freq", c_vp)] + \
+               [("chan_rank", c_i32), ("gate_rank", c_i32), ("w_gate2", c_vp)]
 
 
 class KvCachePlan(C.Structure):
@@ -278,7 +286,14 @@ _SIGS = {
     "b200_hybrid_set_layer": (None, [c_vp, c_i32, C.POINTER(HybridLayer)]),
     "b200_hybrid_set_layer_side": (None, [c_vp, c_i32, C.POINTER(HybridLayer)]),
     "b200_hybrid_set_globals": (None, [c_vp] * 4),
+    "b200_hybrid_set_final_norm": (None, [c_vp, c_vp, c_f32]),
     "b200_hybrid_workspace_bytes": (c_i64, [c_vp]),
+    "b200_stream_norm": (None, [c_vp] * 4 + [c_f32, c_i32, c_f32, c_f32] + [c_vp] * 6 + [c_i32] * 4 + [c_i64]),
+    "b200_depth_mix": (None, [c_vp, c_vp, c_i64, c_vp, c_i32, c_i64, c_i64]),
+    "b200_attn_finish": (None, [c_vp, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp, c_i32, c_i32, c_f32, c_i32, c_f32, c_f32,
+                                c_i32, c_i32, c_i32, c_i32, c_i64]),
+    "b200_lowrank_decay_ex": (None, [c_vp, c_vp, c_i32, c_vp, c_vp, c_f32, c_i32, c_vp, c_i32, c_i32, c_i32, c_i32, c_i64]),
+    "b200_delta_rule_chan": (None, [c_vp] * 4 + [c_i32, c_vp, c_i32, c_vp, c_i32] + [c_vp] * 4 + [c_i32] * 5 + [c_i64]),
     "b200_hybrid_set_workspace": (None, [c_vp, c_vp, c_i64]),
     "b200_hybrid_set_layer_trace": (None, [c_vp, c_vp]),
     "b200_hybrid_step": (None, [c_vp] * 9 + [c_i32] * 4 + [c_vp, c_vp, c_i64]),

@@ -27,6 +27,16 @@
 // Post-norm layer (results are normed on their way into the stream, inputs are not): the sublayers take x rounded to the
 // operand dtype (cast_rows; fp32 runs read x in place): y = mixers(x), x += post_norm(y); y = ff(x), x += ff_post_norm(y), the
 // feed-forward being the routed experts (plus their shared expert) or the dense gated one.
+// Pre-norm layer (each sublayer behind its own norm, added times a factor): h = norm(x) -- RMS or dynamic tanh, with the
+// token shift h[t] += (h[t-1] - h[t]) * shift where the layer has one (stream_norm) --, x += out_scale * mixer(h);
+// h = ff_norm(x), x += ff_scale * ff(h).  With depth weights the layers' results X_0 (embedding) .. X_L are kept side by
+// side, layer i works in place on slot i + 1 (which starts as its input), and depth_mix writes
+// sum_j depth_w[j] X_j into slot i + 2 (the stream for the last layer), which is the next layer's input.
+//   window attention with rotated values, a chunked mask or two score maps: the attention writes fp32, attn_finish
+//                      combines the maps (a_0 - lambda a_1), turns rotated values back, norms per head, scales, gates
+//   delta rule, channel form: [q | k | v | b | low_a | low_g] = h W_in^T ; short_conv_silu ; lowrank_decay (kind 1)
+//                      -> decays per head and key channel ; delta_rule ; gate logits = low_g W_g2^T (fp32 product) ;
+//                      gated_group_norm (sigmoid gate) ; x += . W_o^T
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -55,6 +65,10 @@ struct b200_hybrid {
   std::vector<b200_hybrid_layer> layers;
   std::vector<b200_hybrid_layer> sides;      // side mixer of layer i (sides[i].heads == 0: none)
   const void *embed = nullptr, *final_norm = nullptr, *lm_head = nullptr;
+  const void* final_norm_b = nullptr;        // dynamic-tanh final norm: bias and the scalar inside the tanh
+  float final_norm_alpha = 1.f;
+  float* hist = nullptr;       // [num_layers + 1, T, width] results of the embedding and of every layer (depth weights)
+  float* x0 = nullptr;         // the stream buffer of models without depth weights (x points here)
   uint8_t* ws = nullptr;
   float* trace = nullptr;
   // workspace carve-up
@@ -115,13 +129,23 @@ static int in_rows(const b200_hybrid_layer& l) {
   switch (l.mixer) {
     case B200_MIXER_LATENT_ATTN:
       return l.heads * (l.dim + l.rot_dim) + (l.shared_cache ? 0 : l.kv_rank + l.rot_dim) + (l.gated ? l.heads : 0);
-    case B200_MIXER_DELTA_RULE: return 2 * l.kv_heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads;
-    case B200_MIXER_WINDOW_ATTN:
-      return l.heads * l.dim + l.kv_heads * (l.dim + (l.v_from_k ? 0 : l.vdim)) +
+    case B200_MIXER_DELTA_RULE:
+      if (l.chan_rank > 0) return 2 * l.kv_heads * l.dim + l.heads * l.vdim + l.heads + l.chan_rank + l.gate_rank;
+      return 2 * l.kv_heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads;
+    case B200_MIXER_WINDOW_ATTN: {
+      const int maps = l.score_maps > 1 ? l.score_maps : 1;
+      return maps * l.heads * l.dim +
+             (l.shared_cache ? 0 : maps * l.kv_heads * l.dim + (l.v_from_k ? 0 : l.kv_heads * l.vdim)) +
              (l.gated == 2 ? l.heads * l.vdim : (l.gated ? l.heads : 0));
+    }
     case B200_MIXER_DECAY_ATTN: return 2 * l.heads * l.dim + 2 * l.heads * l.vdim + l.decay_rank;
     default: return 2 * l.heads * l.vdim + 2 * l.kv_heads * l.state + l.heads;
   }
+}
+
+// window attention whose softmax-weighted sums pass attn_finish (fp32 sums, then maps / turn back / norm / gate)
+static bool needs_finish(const b200_hybrid_layer& l) {
+  return l.mixer == B200_MIXER_WINDOW_ATTN && (l.score_maps > 1 || l.v_rot_freq != nullptr || l.diff_norm != 0);
 }
 
 static int64_t carve(b200_hybrid* r, uint8_t* base) {
@@ -136,11 +160,13 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
   for (const b200_hybrid_layer& l : all) {
     proj_n = std::max<size_t>(proj_n, in_rows(l));
     if (l.mixer == B200_MIXER_WINDOW_ATTN) {
-      aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.dim);
+      const int maps = l.score_maps > 1 ? l.score_maps : 1;
+      aux_n = std::max<size_t>(aux_n, static_cast<size_t>(maps) * l.heads * l.dim);
       opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);
+      if (needs_finish(l)) conv_n = std::max<size_t>(conv_n, static_cast<size_t>(maps) * l.heads * l.vdim);
       for (size_t rows = 1; rows <= r->attn_ws_rows; ++rows)
-        attn_bytes = std::max(attn_bytes, window_attn_workspace_bytes(static_cast<int>(rows), l.heads, l.kv_heads, l.vdim,
-                                                                      l.window, l.keep_first));
+        attn_bytes = std::max(attn_bytes, window_attn_workspace_bytes(static_cast<int>(rows), maps * l.heads,
+                                                                      maps * l.kv_heads, l.vdim, l.window, l.keep_first));
     } else if (l.mixer == B200_MIXER_DECAY_ATTN) {
       aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.vdim);
       opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);
@@ -154,8 +180,10 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
     } else {
       aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.vdim);
       opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);
+      // (channel form of the delta rule: the decays and the gate logits follow the convolved rows)
       conv_n = std::max<size_t>(conv_n, l.mixer == B200_MIXER_DELTA_RULE
-                                            ? 2 * static_cast<size_t>(l.kv_heads) * l.dim + static_cast<size_t>(l.heads) * l.vdim
+                                            ? 2 * static_cast<size_t>(l.kv_heads) * l.dim + static_cast<size_t>(l.heads) * l.vdim +
+                                                  (l.chan_rank > 0 ? static_cast<size_t>(l.heads) * (l.dim + l.vdim) : 0)
                                             : static_cast<size_t>(l.heads) * l.vdim + 2 * static_cast<size_t>(l.kv_heads) * l.state);
     }
     if (l.experts > 0) {
@@ -172,7 +200,10 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
     off = up256(off + bytes);
     return p;
   };
-  r->x = (float*)take(T * c.width * 4);
+  bool depth = false;
+  for (const b200_hybrid_layer& l : r->layers) depth = depth || l.depth_w != nullptr;
+  r->x0 = r->x = (float*)take(T * c.width * 4);
+  r->hist = depth ? (float*)take((static_cast<size_t>(c.num_layers) + 1) * T * c.width * 4) : nullptr;
   r->y = (float*)take(T * c.width * 4);
   r->h = take(T * c.width * es);
   r->proj = (float*)take(T * proj_n * 4);
@@ -231,7 +262,9 @@ static bool mixer_ok(const b200_hybrid_layer* l) {
   if (l->mixer == B200_MIXER_WINDOW_ATTN)
     return ok && l->kv_heads > 0 && l->heads % l->kv_heads == 0 && l->dim > 0 && l->rot_dims % 2 == 0 &&
            l->rot_dims <= l->dim && (l->rot_dims == 0 || l->rot_freq) && l->kv_cache && l->v_cache &&
-           (!l->v_from_k || l->vdim == l->dim) && l->gated >= 0 && l->gated <= 2;
+           (!l->v_from_k || l->vdim == l->dim) && l->gated >= 0 && l->gated <= 2 && l->score_maps >= 0 &&
+           l->score_maps <= 2 && (l->score_maps < 2 || (!l->v_from_k && !l->sink)) && l->chunk >= 0 &&
+           (!l->v_rot_freq || (l->vdim % 2 == 0 && !l->v_from_k));
   if (l->mixer == B200_MIXER_DECAY_ATTN)
     return ok && l->dim > 0 && l->dim <= 256 && l->rec_state && l->norm_groups > 0 &&
            (l->heads * l->vdim) % l->norm_groups == 0 && (l->out_norm_period == 0 || l->out_norm_w) &&
@@ -261,7 +294,13 @@ void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_laye
   else if (l->layout == B200_LAYOUT_POSTNORM)
     ok = ok && l->post_norm_w && ((l->shared_ff == 0 && l->experts == 0) || l->ff_post_norm_w);
   else
-    ok = ok && l->norm_w && l->layout == B200_LAYOUT_PARALLEL;
+    ok = ok && l->norm_w && (l->layout == B200_LAYOUT_PARALLEL || l->layout == B200_LAYOUT_PRENORM);
+  if (l->layout == B200_LAYOUT_PRENORM)
+    ok = ok && ((l->shared_ff == 0 && l->experts == 0) || l->ff_norm_w) && (l->experts == 0 || l->ff_scale == 1.f);
+  ok = ok && (l->norm_kind == B200_NORM_RMS || l->norm_kind == B200_NORM_DYNTANH) && (!l->shift_w || l->shift_state) &&
+       ((!l->shift_w && !l->depth_w && !l->ff_up_bias && !l->ff_down_bias && l->norm_kind == B200_NORM_RMS) ||
+        l->layout == B200_LAYOUT_PRENORM) &&
+       ((!l->ff_up_bias && !l->ff_down_bias) || (l->shared_ff > 0 && l->shared_act == 1 && !l->shared_gated));
   if (l->mixer == B200_MIXER_WINDOW_ATTN || l->mixer == B200_MIXER_DECAY_ATTN)
     ok = ok && mixer_ok(l);
   else if (l->mixer == B200_MIXER_LATENT_ATTN)
@@ -270,7 +309,8 @@ void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_laye
          (l->gated == 0 || l->gated == 1) && (!l->shared_cache || l->rot_dim == 0);
   else if (l->mixer == B200_MIXER_DELTA_RULE)
     ok = ok && l->kv_heads > 0 && l->heads % l->kv_heads == 0 && l->dim > 0 && l->conv_taps >= 1 && l->conv_w &&
-         l->conv_state && l->rec_state && l->a_log && l->dt_bias && l->out_norm_w;
+         l->conv_state && l->rec_state && l->a_log && l->dt_bias && l->out_norm_w && l->chan_rank >= 0 &&
+         l->gate_rank >= 0 && (l->chan_rank == 0 ? l->gate_rank == 0 : (l->w_decay2 && l->gate_rank > 0 && l->w_gate2));
   else if (l->mixer == B200_MIXER_SSD)
     ok = ok && l->kv_heads > 0 && l->heads % l->kv_heads == 0 && l->state > 0 && l->conv_taps >= 1 && l->conv_w &&
          l->conv_state && l->rec_state && l->a_log && l->dt_bias && l->out_norm_w && l->norm_groups > 0 &&
@@ -302,6 +342,11 @@ void b200_hybrid_set_globals(b200_hybrid* r, const void* embed, const void* fina
   r->lm_head = lm_head;
 }
 
+void b200_hybrid_set_final_norm(b200_hybrid* r, const void* bias, float alpha) {
+  r->final_norm_b = bias;
+  r->final_norm_alpha = alpha;
+}
+
 int64_t b200_hybrid_workspace_bytes(const b200_hybrid* r) {
   b200_hybrid tmp;
   tmp.cfg = r->cfg;
@@ -313,6 +358,12 @@ int64_t b200_hybrid_workspace_bytes(const b200_hybrid* r) {
 void b200_hybrid_set_workspace(b200_hybrid* r, void* workspace, int64_t bytes) {
   uint8_t* base = reinterpret_cast<uint8_t*>(up256(reinterpret_cast<size_t>(workspace)));
   const int64_t need = carve(r, base);
+  if (r->hist)
+    for (const b200_hybrid_layer& l : r->layers)
+      if (l.layout != B200_LAYOUT_PRENORM) {
+        set_error(1, "hybrid_set_workspace: depth weights need every layer in the pre-norm layout");
+        return;
+      }
   if (need + (base - reinterpret_cast<uint8_t*>(workspace)) > bytes) {
     set_error(1, "hybrid_set_workspace: workspace too small (set every layer before asking for its size)");
     return;
@@ -393,10 +444,28 @@ static void mixer_delta(b200_hybrid* r, const b200_hybrid_layer& l, const uint32
   const float* k = r->conv + nq;
   const float* v = r->conv + 2 * nq;
   const float* b_raw = r->proj + nconv;
+  if (l.chan_rank > 0) {
+    // decays per head and key channel, and the gate's logits, from the two low-rank halves that close the projection
+    // row; the second factors are fp32 whatever the operand dtype (what enters the recurrence is not rounded)
+    const int nd = H * l.dim;
+    float* decay = r->conv + static_cast<size_t>(T) * nconv;
+    float* gate2 = decay + static_cast<size_t>(T) * nd;
+    const float* low_a = b_raw + H;
+    const float* low_g = low_a + l.chan_rank;
+    launch_lowrank_decay(decay, low_a, n_in, (const float*)l.w_decay2, (const float*)l.dt_bias, 1.f, (const float*)l.a_log,
+                         l.dim, T, nd, l.chan_rank, st);
+    launch_delta_rule(r->aux, q, k, v, nconv, b_raw, nullptr, n_in, nullptr, nullptr, decay, nd, (float*)l.rec_state,
+                      state_slots, cu, ctx, B, H, Hk, l.dim, l.vdim, st);
+    gemm_f32out(low_g, n_in, 0, l.w_gate2, l.gate_rank, 0, gate2, nv, 0, T, nv, l.gate_rank, 1, 0.f, 0, 1, st);
+    launch_gated_group_norm(r->opa, r->aux, nv, gate2, nv, (const float*)l.out_norm_w, l.vdim, T, nv, l.vdim, c.norm_eps,
+                            0, 1, c.dt, st);
+    gemm_f32out_scaled(r->opa, nv, 0, l.w_o, nv, 0, dst, c.width, 0, T, c.width, nv, 1, alpha, beta, 0, c.dt, st);
+    return;
+  }
   const float* a_raw = b_raw + H;
   const float* gate = a_raw + H;
-  launch_delta_rule(r->aux, q, k, v, nconv, b_raw, a_raw, n_in, (const float*)l.a_log, (const float*)l.dt_bias,
-                    (float*)l.rec_state, state_slots, cu, ctx, B, H, Hk, l.dim, l.vdim, st);
+  launch_delta_rule(r->aux, q, k, v, nconv, b_raw, a_raw, n_in, (const float*)l.a_log, (const float*)l.dt_bias, nullptr,
+                    0, (float*)l.rec_state, state_slots, cu, ctx, B, H, Hk, l.dim, l.vdim, st);
   launch_gated_group_norm(r->opa, r->aux, nv, gate, n_in, (const float*)l.out_norm_w, l.vdim, T, nv, l.vdim, c.norm_eps,
                           0, 0, c.dt, st);
   gemm_f32out_scaled(r->opa, nv, 0, l.w_o, nv, 0, dst, c.width, 0, T, c.width, nv, 1, alpha, beta, 0, c.dt, st);
@@ -424,21 +493,39 @@ static void mixer_window(b200_hybrid* r, const b200_hybrid_layer& l, const int64
                          float* dst, float alpha, float beta, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, G = l.kv_heads, n_in = in_rows(l), nv = H * l.vdim;
+  const int maps = l.score_maps > 1 ? l.score_maps : 1;       // the maps' heads lie one map after the other
+  const bool finish = needs_finish(l);
   gemm_f32out(r->hin, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
   b200_attn_options opt;
+  std::memset(&opt, 0, sizeof(opt));
   opt.head_norm = l.head_norm;
   opt.v_from_k = l.v_from_k;
   opt.q_temp_every = l.q_temp_every;
   opt.q_temp_coef = l.q_temp_coef;
   opt.gate_elems = l.gated == 2;
   opt.dist_slopes = (const float*)l.dist_slopes;
+  opt.rot_half = l.rot_half;
+  opt.rot_mag = l.rot_mag;
+  opt.v_rot_freq = l.v_rot_freq;
+  opt.v_heads = G;
+  opt.chunk = l.chunk;
+  opt.out_f32 = finish;
+  opt.no_cache = l.shared_cache;
   launch_window_attn_prep(r->proj, n_in, (const float*)l.in_bias, (const float*)l.q_norm_w, (const float*)l.k_norm_w,
-                          l.rot_freq, positions, slots, r->aux, l.kv_cache, l.v_cache, T, H, G, l.dim, l.vdim, l.rot_dims,
-                          c.norm_eps, c.dt, &opt, st);
-  const float* gate = l.gated ? r->proj + H * l.dim + G * (l.dim + (l.v_from_k ? 0 : l.vdim)) : nullptr;
-  launch_window_attn(r->opa, r->aux, l.kv_cache, l.v_cache, (const float*)l.sink, gate, n_in, cu, ctx, bt, max_blocks, B,
-                     T, H, G, l.dim, l.vdim, l.window, l.keep_first, l.scale, l.softcap, c.dt,
-                     static_cast<size_t>(T) <= r->attn_ws_rows ? r->attn_ws : nullptr, &opt, st);
+                          l.rot_freq, positions, slots, r->aux, l.kv_cache, l.v_cache, T, maps * H, maps * G, l.dim,
+                          l.vdim, l.rot_dims, c.norm_eps, c.dt, &opt, st);
+  const float* gate = l.gated ? r->proj + (n_in - (l.gated == 2 ? nv : H)) : nullptr;     // the gate logits close the row
+  void* ws = static_cast<size_t>(T) <= r->attn_ws_rows ? r->attn_ws : nullptr;
+  if (finish) {
+    // fp32 sums of every map, then one kernel for all that follows them
+    launch_window_attn(r->conv, r->aux, l.kv_cache, l.v_cache, (const float*)l.sink, nullptr, 0, cu, ctx, bt, max_blocks, B,
+                       T, maps * H, maps * G, l.dim, l.vdim, l.window, l.keep_first, l.scale, l.softcap, c.dt, ws, &opt, st);
+    launch_attn_finish(r->opa, r->conv, gate, n_in, l.gated == 2, positions, l.v_rot_freq, l.rot_half, maps, l.diff_lambda,
+                       l.diff_norm, c.norm_eps, maps > 1 ? l.diff_out_scale : 1.f, T, H, l.vdim, c.dt, st);
+  } else {
+    launch_window_attn(r->opa, r->aux, l.kv_cache, l.v_cache, (const float*)l.sink, gate, n_in, cu, ctx, bt, max_blocks, B,
+                       T, H, G, l.dim, l.vdim, l.window, l.keep_first, l.scale, l.softcap, c.dt, ws, &opt, st);
+  }
   gemm_f32out_scaled(r->opa, nv, 0, l.w_o, nv, 0, dst, c.width, 0, T, c.width, nv, 1, alpha, beta, 0, c.dt, st);
   if (l.o_bias) launch_bias_rows(dst, (const float*)l.o_bias, alpha, T, c.width, st);
 }
@@ -454,8 +541,8 @@ static void mixer_decay(b200_hybrid* r, const b200_hybrid_layer& l, const uint32
   const float* gate = v + nv;
   const float* chan = nullptr;
   if (l.decay_rank > 0) {
-    launch_lowrank_decay(r->conv, gate + nv, n_in, (const float*)l.w_decay2, (const float*)l.decay_bias, l.decay_tau, T,
-                         nk, l.decay_rank, st);
+    launch_lowrank_decay(r->conv, gate + nv, n_in, (const float*)l.w_decay2, (const float*)l.decay_bias, l.decay_tau,
+                         nullptr, 1, T, nk, l.decay_rank, st);
     chan = r->conv;
   }
   launch_decay_attn(r->aux, q, k, v, n_in, chan ? nullptr : (const float*)l.head_decay, chan, nk, l.q_scale, l.k_scale,
@@ -496,8 +583,9 @@ static void dense_ffn(b200_hybrid* r, const b200_hybrid_layer& l, int T, cudaStr
 
 // routed experts and their shared expert: dst = (accumulate ? dst : 0) + experts(h) + shared(h).  `ident` / `ident_f32`:
 // the rows that identity experts return (the sublayer's input before any rounding, where the layer has it in fp32).
+// `scale` multiplies the shared / dense part (routed experts take none).
 static void feed_forward(b200_hybrid* r, const b200_hybrid_layer& l, int T, float* dst, bool accumulate, const void* ident,
-                         int ident_f32, cudaStream_t st) {
+                         int ident_f32, cudaStream_t st, float scale = 1.f) {
   const b200_hybrid_config& c = r->cfg;
   if (l.experts > 0) {
     const int all = l.experts + l.identity_experts;
@@ -516,9 +604,11 @@ static void feed_forward(b200_hybrid* r, const b200_hybrid_layer& l, int T, floa
     if (l.shared_act == 0)
       launch_silu_mul_f32(r->sha, r->sh, T, l.shared_ff, c.dt, st);
     else
-      launch_relu2_f32(r->sha, r->sh, rows, T, l.shared_ff, l.shared_gated ? l.shared_ff : -1, c.dt, st);
-    gemm_f32out(r->sha, l.shared_ff, 0, l.w_shared_down, l.shared_ff, 0, dst, c.width, 0, T, c.width, l.shared_ff, 1,
-                accumulate ? 1.f : 0.f, 0, c.dt, st);
+      launch_relu2_f32(r->sha, r->sh, rows, T, l.shared_ff, l.shared_gated ? l.shared_ff : -1,
+                       (const float*)l.ff_up_bias, c.dt, st);
+    gemm_f32out_scaled(r->sha, l.shared_ff, 0, l.w_shared_down, l.shared_ff, 0, dst, c.width, 0, T, c.width, l.shared_ff,
+                       1, scale, accumulate ? 1.f : 0.f, 0, c.dt, st);
+    if (l.ff_down_bias) launch_bias_rows(dst, (const float*)l.ff_down_bias, scale, T, c.width, st);
   }
 }
 
@@ -539,8 +629,15 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
   const long long launches0 = launch_count();
   // the sublayers of post-norm layers take the un-normed stream: in bf16 runs the kernel that last wrote x also leaves its rounding in h
   const bool first_reads_stream = r->layers[0].layout == B200_LAYOUT_POSTNORM && !c.dt;
+  // with depth weights the results of the embedding and of every layer lie side by side; layer i works in slot i + 1
+  const size_t hstride = static_cast<size_t>(c.max_tokens) * c.width, xbytes = static_cast<size_t>(T) * c.width * 4;
+  r->x = r->hist ? r->hist : r->x0;
   launch_embed_f32(r->x, r->embed, input_ids, positions, c.embed_pos_base, T, c.width, c.vocab, c.embed_scale, c.dt,
                    first_reads_stream ? r->h : nullptr, st);
+  if (r->hist) {
+    cudaMemcpyAsync(r->hist + hstride, r->hist, xbytes, cudaMemcpyDeviceToDevice, st);     // layer 0 starts from X_0
+    r->x = r->hist + hstride;
+  }
   bool h_is_x = first_reads_stream;          // h holds the bf16 rounding of the current x
   for (int i = 0; i < c.num_layers; ++i) {
     const b200_hybrid_layer& l = r->layers[i];
@@ -575,6 +672,33 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
       continue;
     }
     h_is_x = false;
+    if (l.layout == B200_LAYOUT_PRENORM) {
+      launch_stream_norm(r->h, r->x, (const float*)l.norm_w, (const float*)l.norm_b, l.norm_alpha, l.norm_kind, c.norm_eps,
+                         c.norm_weight_offset, nullptr, (const float*)l.shift_w, (float*)l.shift_state, state_slots, cu,
+                         ctx, B, T, c.width, c.dt, st);
+      run_mixer(r, l, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->x, l.out_scale,
+                1.f, st);
+      if (side.heads > 0)
+        run_mixer(r, side, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->x,
+                  side.out_scale, 1.f, st);
+      if (l.experts > 0 || l.shared_ff > 0) {
+        launch_stream_norm(r->h, r->x, (const float*)l.ff_norm_w, (const float*)l.ff_norm_b, l.ff_norm_alpha, l.norm_kind,
+                           c.norm_eps, c.norm_weight_offset, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, T,
+                           c.width, c.dt, st);
+        feed_forward(r, l, T, r->x, true, r->h, 0, st, l.ff_scale);
+      }
+      if (r->hist) {
+        // what goes on: the weighted sum of the results so far, or (a layer without weights) this layer's result
+        float* next = i + 1 < c.num_layers ? r->hist + static_cast<size_t>(i + 2) * hstride : r->x0;
+        if (l.depth_w) launch_depth_mix(next, r->hist, hstride, (const float*)l.depth_w, i + 2, static_cast<size_t>(T) * c.width, st);
+        else cudaMemcpyAsync(next, r->x, xbytes, cudaMemcpyDeviceToDevice, st);
+        r->x = next;
+      }
+      if (r->trace)
+        cudaMemcpyAsync(r->trace + static_cast<size_t>(i) * c.max_tokens * c.width, r->x, xbytes, cudaMemcpyDeviceToDevice,
+                        st);
+      continue;
+    }
     launch_resid_rmsnorm(r->h, r->x, (const float*)l.norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, nullptr,
                          c.dt, st);
     if (l.layout == B200_LAYOUT_SANDWICH) {
@@ -605,8 +729,13 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
                       static_cast<size_t>(T) * c.width * 4, cudaMemcpyDeviceToDevice, st);
   }
   if (num_out > 0) {
-    launch_resid_rmsnorm(r->hr, r->x, (const float*)r->final_norm, num_out, c.width, c.norm_eps, c.norm_weight_offset,
-                         out_rows, c.dt, st);
+    if (c.final_norm_kind == B200_NORM_RMS)
+      launch_resid_rmsnorm(r->hr, r->x, (const float*)r->final_norm, num_out, c.width, c.norm_eps, c.norm_weight_offset,
+                           out_rows, c.dt, st);
+    else
+      launch_stream_norm(r->hr, r->x, (const float*)r->final_norm, (const float*)r->final_norm_b, r->final_norm_alpha,
+                         c.final_norm_kind, c.norm_eps, c.norm_weight_offset, out_rows, nullptr, nullptr, nullptr, nullptr,
+                         nullptr, 0, num_out, c.width, c.dt, st);
     float* lg = logits ? logits : r->logits;
     gemm_f32out(r->hr, c.width, 0, r->lm_head, c.width, 0, lg, c.vocab, 0, num_out, c.vocab, c.width, 1, 0.f, 0, c.dt,
                 st);

@@ -9,7 +9,9 @@
 //                     launch rolls the state forward.
 //   delta_rule      : per head, S [dim, vdim]:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                     with q, k unit-normalised per head (q also times dim^-1/2), beta = sigmoid(b),
-//                     g = exp(-exp(a_log) * softplus(a + dt_bias)).  state [slots, heads, dim, vdim].
+//                     g = exp(-exp(a_log) * softplus(a + dt_bias)).  state [slots, heads, dim, vdim].  In the
+//                     channel form g is one decay per head AND key channel (row i of S is multiplied by g[i]), handed
+//                     in ready-made (lowrank_decay kind 1 makes it from a low-rank projection).
 //   ssd_scan        : per head, S [nstate, vdim]:  dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(a_log) dt) S + dt B x^T;
 //                     y = S^T C + D x.  state [slots, heads, nstate, vdim].
 //   decay_attn      : per head, S [dim, vdim]:  S <- diag(a_t) S + k_t v_t^T;  o_t = S^T q_t  (linear attention with a decayed
@@ -114,16 +116,21 @@ constexpr int kScanThreads = 128, kScanCols = kScanThreads / kRowSplit;      // 
 
 // grid = (column blocks, heads, sequences); block = 128 threads = 16 columns x kRowSplit lanes.  DK = compile-time
 // bound of `dim`; a lane holds the rows i = j * kRowSplit + part of its column.
-template <int DK>
+// CHAN: the decay is one value per head, key channel and token, read ready-made from chan_decay [T, heads, dim] (row
+// stride ld_decay; a_raw, a_log and dt_bias are not used); otherwise one value per head and token computed here.
+template <int DK, bool CHAN>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k,
                   const float* __restrict__ v, int ld, const float* __restrict__ b_raw,
                   const float* __restrict__ a_raw, int ld_ba, const float* __restrict__ a_log,
-                  const float* __restrict__ dt_bias, float* __restrict__ state, const int32_t* __restrict__ slots,
+                  const float* __restrict__ dt_bias, const float* __restrict__ chan_decay, int ld_decay,
+                  float* __restrict__ state, const int32_t* __restrict__ slots,
                   const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int heads, int kv_heads, int dim,
                   int vdim) {
-  constexpr int RS = kRowSplit, NR = DK / RS, kChunk = chunk_for(DK);
+  // a third staged row set halves the tokens per pass where the rows are long (static shared memory stays under 48 KB)
+  constexpr int RS = kRowSplit, NR = DK / RS, kChunk = (CHAN && DK >= 64) ? chunk_for(DK) / 2 : chunk_for(DK);
   __shared__ float ks[2][kChunk][DK], qs[2][kChunk][DK], vs[2][kChunk][kScanCols], gs[2][kChunk], bs[2][kChunk];
+  __shared__ float as[CHAN ? 2 : 1][CHAN ? kChunk : 1][CHAN ? DK : 1];
   const int h = blockIdx.y, b = blockIdx.z;
   const int part = threadIdx.x % RS;
   const int col = blockIdx.x * (blockDim.x / RS) + threadIdx.x / RS;
@@ -139,10 +146,14 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
     const int i = j * RS + part;
     s[j] = (!fresh && live && i < dim) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
   }
-  const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], qscale = rsqrtf(static_cast<float>(dim));
+  const float neg_a = CHAN ? 0.f : -expf(a_log[h]), dtb = CHAN ? 0.f : dt_bias[h];
+  const float qscale = rsqrtf(static_cast<float>(dim));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   if (dim < DK)                                                           // the padding past `dim` stays zero
-    for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads) (&ks[0][0][0])[e] = (&qs[0][0][0])[e] = 0.f;
+    for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads) {
+      (&ks[0][0][0])[e] = (&qs[0][0][0])[e] = 0.f;
+      if (CHAN) (&as[0][0][0])[e] = 0.f;
+    }
   for (int e = threadIdx.x; e < 2 * kChunk * kScanCols; e += kScanThreads) (&vs[0][0][0])[e] = 0.f;
   __syncthreads();
   // raw rows of one pass -> buffer `buf` (asynchronous; committed as one group)
@@ -152,6 +163,7 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
       const int r = e / dim, i = e - r * dim;
       cp_async4(&ks[buf][r][i], k + static_cast<size_t>(c0 + r) * ld + hk * dim + i);
       cp_async4(&qs[buf][r][i], q + static_cast<size_t>(c0 + r) * ld + hk * dim + i);
+      if (CHAN) cp_async4(&as[buf][r][i], chan_decay + static_cast<size_t>(c0 + r) * ld_decay + h * dim + i);
     }
     for (int e = threadIdx.x; e < n * kScanCols; e += kScanThreads) {
       const int r = e / kScanCols, c = blockIdx.x * kScanCols + e % kScanCols;
@@ -159,7 +171,7 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
     }
     if (threadIdx.x < n) {
       cp_async4(&bs[buf][threadIdx.x], b_raw + static_cast<size_t>(c0 + threadIdx.x) * ld_ba + h);
-      cp_async4(&gs[buf][threadIdx.x], a_raw + static_cast<size_t>(c0 + threadIdx.x) * ld_ba + h);
+      if (!CHAN) cp_async4(&gs[buf][threadIdx.x], a_raw + static_cast<size_t>(c0 + threadIdx.x) * ld_ba + h);
     }
     cp_async_commit();
   };
@@ -190,20 +202,20 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
       }
       if (lane == 0) {
         bs[buf][r] = sigmoid_f(bs[buf][r]);
-        gs[buf][r] = expf(neg_a * softplus_f(gs[buf][r] + dtb));
+        if (!CHAN) gs[buf][r] = expf(neg_a * softplus_f(gs[buf][r] + dtb));
       }
     }
     __syncthreads();
     for (int r = 0; r < n; ++r) {          // every lane runs the shuffles; dead columns carry zeros
       const float vv = vs[buf][r][threadIdx.x / RS];
-      const float g = gs[buf][r];
+      const float g = CHAN ? 0.f : gs[buf][r];
       float d0 = 0.f, d1 = 0.f;
 #pragma unroll
       for (int j = 0; j < NR; j += 2) {
-        s[j] *= g;
+        s[j] *= CHAN ? as[CHAN ? buf : 0][CHAN ? r : 0][CHAN ? j * RS + part : 0] : g;
         d0 += ks[buf][r][j * RS + part] * s[j];
         if (j + 1 < NR) {
-          s[j + 1] *= g;
+          s[j + 1] *= CHAN ? as[CHAN ? buf : 0][CHAN ? r : 0][CHAN ? (j + 1) * RS + part : 0] : g;
           d1 += ks[buf][r][(j + 1) * RS + part] * s[j + 1];
         }
       }
@@ -330,12 +342,15 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
 
 // out[t, c] = sigmoid(z)^(1 / tau) with z = bias[c] + sum_r w2[c, r] * low[t, r]: the per-channel decay of gated linear
 // attention from the low-rank half of its projection.  Computed as exp(log sigmoid(z) / tau), all fp32.
+// a_log != NULL (kind 1): out[t, c] = exp(-exp(a_log[c / a_period]) * softplus(z)), the decay of a gated delta rule per
+// head and key channel.
 // grid = (channel blocks, token tiles): a thread owns one channel and kDecayTile tokens; the tokens' low-rank rows sit in
 // shared memory, the channel's row of w2 is read once per tile (each thread whole sectors), the stores are coalesced.
 constexpr int kDecayTile = 16;
 __global__ void __launch_bounds__(256)
 lowrank_decay_kernel(float* __restrict__ out, const float* __restrict__ low, int ld_low, const float* __restrict__ w2,
-                     const float* __restrict__ bias, float inv_tau, int T, int C, int rank) {
+                     const float* __restrict__ bias, float inv_tau, const float* __restrict__ a_log, int a_period, int T,
+                     int C, int rank) {
   extern __shared__ float lr[];          // [kDecayTile][rank]
   const int t0 = blockIdx.y * kDecayTile, nt = min(kDecayTile, T - t0);
   for (int e = threadIdx.x; e < nt * rank; e += blockDim.x)
@@ -356,6 +371,10 @@ lowrank_decay_kernel(float* __restrict__ out, const float* __restrict__ low, int
 #pragma unroll
   for (int i = 0; i < kDecayTile; ++i) {
     if (i >= nt) break;
+    if (a_log) {
+      out[static_cast<size_t>(t0 + i) * C + c] = expf(-expf(a_log[c / a_period]) * softplus_f(z[i]));
+      continue;
+    }
     const float ls = z[i] >= 0.f ? -log1pf(expf(-z[i])) : z[i] - log1pf(expf(z[i]));
     out[static_cast<size_t>(t0 + i) * C + c] = expf(ls * inv_tau);
   }
@@ -540,25 +559,31 @@ void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const 
 }
 
 void launch_delta_rule(float* out, const float* q, const float* k, const float* v, int ld, const float* b_raw,
-                       const float* a_raw, int ld_ba, const float* a_log, const float* dt_bias, float* state,
-                       const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads,
-                       int kv_heads, int dim, int vdim, cudaStream_t st_) {
+                       const float* a_raw, int ld_ba, const float* a_log, const float* dt_bias, const float* chan_decay,
+                       int ld_decay, float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx,
+                       int num_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t st_) {
   if (num_seqs <= 0) return;
   const int th = kScanThreads;
   const dim3 grid((vdim + kScanCols - 1) / kScanCols, heads, num_seqs);
-#define B200_DELTA(DK)                                                                                              \
-  delta_rule_kernel<DK><<<grid, th, 0, st_>>>(out, q, k, v, ld, b_raw, a_raw, ld_ba, a_log, dt_bias, state, slots, \
-                                              cu, ctx, heads, kv_heads, dim, vdim)
-  if (dim <= 16) B200_DELTA(16);
-  else if (dim <= 32) B200_DELTA(32);
-  else if (dim <= 64) B200_DELTA(64);
-  else if (dim <= 128) B200_DELTA(128);
-  else if (dim <= 256) B200_DELTA(256);
+#define B200_DELTA2(DK, CH)                                                                                        \
+  delta_rule_kernel<DK, CH><<<grid, th, 0, st_>>>(out, q, k, v, ld, b_raw, a_raw, ld_ba, a_log, dt_bias, chan_decay, \
+                                                  ld_decay, state, slots, cu, ctx, heads, kv_heads, dim, vdim)
+#define B200_DELTA(DK)                     \
+  {                                        \
+    if (chan_decay) B200_DELTA2(DK, true); \
+    else B200_DELTA2(DK, false);           \
+  }
+  if (dim <= 16) B200_DELTA(16)
+  else if (dim <= 32) B200_DELTA(32)
+  else if (dim <= 64) B200_DELTA(64)
+  else if (dim <= 128) B200_DELTA(128)
+  else if (dim <= 256) B200_DELTA(256)
   else {
     set_error(1, "delta_rule: key dimension above 256 is not supported");
     return;
   }
 #undef B200_DELTA
+#undef B200_DELTA2
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -586,16 +611,16 @@ void launch_ssd_scan(float* out, const float* x, const float* Bm, const float* C
 }
 
 
-void launch_lowrank_decay(float* out, const float* low, int ld_low, const float* w2, const float* bias, float tau, int T,
-                          int C, int rank, cudaStream_t st_) {
+void launch_lowrank_decay(float* out, const float* low, int ld_low, const float* w2, const float* bias, float tau,
+                          const float* a_log, int a_period, int T, int C, int rank, cudaStream_t st_) {
   if (T <= 0 || C <= 0) return;
   if (rank <= 0 || rank > 512) {
     set_error(1, "lowrank_decay: the rank must be between 1 and 512");
     return;
   }
   const dim3 grid((C + 255) / 256, (T + kDecayTile - 1) / kDecayTile);
-  lowrank_decay_kernel<<<grid, 256, static_cast<size_t>(kDecayTile) * rank * 4, st_>>>(out, low, ld_low, w2, bias,
-                                                                                       1.f / tau, T, C, rank);
+  lowrank_decay_kernel<<<grid, 256, static_cast<size_t>(kDecayTile) * rank * 4, st_>>>(
+      out, low, ld_low, w2, bias, a_log ? 0.f : 1.f / tau, a_log, a_period > 0 ? a_period : 1, T, C, rank);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -646,8 +671,20 @@ void b200_delta_rule(float* out, const float* q, const float* k, const float* v,
   B200_CHECK_ARG(out && q && k && v && b_raw && a_raw && a_log && dt_bias && state && state_slots && cu_seqlens_q &&
                      context_lens && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0,
                  "delta_rule: bad arguments");
-  b200::launch_delta_rule(out, q, k, v, ld, b_raw, a_raw, ld_ba, a_log, dt_bias, state, state_slots, cu_seqlens_q,
-                          context_lens, num_seqs, heads, kv_heads, dim, vdim, reinterpret_cast<cudaStream_t>(stream));
+  b200::launch_delta_rule(out, q, k, v, ld, b_raw, a_raw, ld_ba, a_log, dt_bias, nullptr, 0, state, state_slots,
+                          cu_seqlens_q, context_lens, num_seqs, heads, kv_heads, dim, vdim,
+                          reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_delta_rule_chan(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* b_raw,
+                          int32_t ld_b, const float* chan_decay, int32_t ld_decay, float* state,
+                          const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                          int32_t num_seqs, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int64_t stream) {
+  B200_CHECK_ARG(out && q && k && v && b_raw && chan_decay && state && state_slots && cu_seqlens_q && context_lens &&
+                     heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0,
+                 "delta_rule_chan: bad arguments");
+  b200::launch_delta_rule(out, q, k, v, ld, b_raw, nullptr, ld_b, nullptr, nullptr, chan_decay, ld_decay, state,
+                          state_slots, cu_seqlens_q, context_lens, num_seqs, heads, kv_heads, dim, vdim,
+                          reinterpret_cast<cudaStream_t>(stream));
 }
 void b200_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm, int32_t ld, const float* dt_raw,
                    int32_t ld_dt, const float* a_log, const float* dt_bias, const float* d_skip, float* state,
@@ -662,8 +699,17 @@ void b200_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm,
 void b200_lowrank_decay(float* out, const float* low, int32_t ld_low, const float* w2, const float* bias, float tau,
                          int32_t num_tokens, int32_t channels, int32_t rank, int64_t stream) {
   B200_CHECK_ARG(out && low && w2 && tau > 0.f && channels > 0 && rank > 0 && rank <= 512, "lowrank_decay: bad arguments (rank up to 512)");
-  b200::launch_lowrank_decay(out, low, ld_low, w2, bias, tau, num_tokens, channels, rank,
+  b200::launch_lowrank_decay(out, low, ld_low, w2, bias, tau, nullptr, 1, num_tokens, channels, rank,
                              reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_lowrank_decay_ex(float* out, const float* low, int32_t ld_low, const float* w2, const float* bias, float tau,
+                           int32_t kind, const float* a_log, int32_t a_period, int32_t num_tokens, int32_t channels,
+                           int32_t rank, int64_t stream) {
+  B200_CHECK_ARG(out && low && w2 && channels > 0 && rank > 0 && rank <= 512 &&
+                     (kind == 0 ? tau > 0.f : (kind == 1 && a_log && a_period > 0 && channels % a_period == 0)),
+                 "lowrank_decay: bad arguments (rank up to 512; kind 0 needs tau, kind 1 a_log)");
+  b200::launch_lowrank_decay(out, low, ld_low, w2, bias, tau, kind == 1 ? a_log : nullptr, a_period, num_tokens, channels,
+                             rank, reinterpret_cast<cudaStream_t>(stream));
 }
 void b200_decay_attn(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* head_decay,
                      const float* chan_decay, int32_t ld_decay, float q_scale, float k_scale, int32_t act, float* state,

@@ -85,7 +85,15 @@ void launch_bias_rows(float* y, const float* bias, float scale, int T, int n, cu
 void launch_cast_rows(void* out, const float* in, int ld_in, int T, int n, int dt, cudaStream_t st);
 void launch_silu_mul_f32(void* out, const float* gate_up, int T, int ff, int dt, cudaStream_t st);
 // out [T, ff] = relu(up[t, d])^2 (* sigmoid(up[t, gate_col]) when gate_col >= 0); up fp32 with row stride ld
-void launch_relu2_f32(void* out, const float* up, int ld, int T, int ff, int gate_col, int dt, cudaStream_t st);
+// bias (may be NULL): fp32 [ff], added before the activation
+void launch_relu2_f32(void* out, const float* up, int ld, int T, int ff, int gate_col, const float* bias, int dt,
+                      cudaStream_t st);
+// norm of the stream (kind B200_NORM_*), optionally followed by the token shift (see b200_stream_norm)
+void launch_stream_norm(void* out, const float* x, const float* w, const float* bias, float alpha, int kind, float eps,
+                        float w_offset, const uint32_t* rows, const float* shift_w, float* shift_state,
+                        const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int T, int width,
+                        int dt, cudaStream_t st);
+void launch_depth_mix(float* out, const float* hist, size_t stride, const float* w, int count, size_t n, cudaStream_t st);
 
 void launch_latent_prep(const float* qc, int ldq, void* q_plain, float* q_full, void* cache, const float* latent_norm_w,
                         const double* rot_freq, float rot_mag, const int64_t* positions, const int64_t* slots, int T,
@@ -107,21 +115,28 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
                         int dim, int vdim, int window, int keep_first, float scale, float softcap, int dt,
                         void* workspace, const b200_attn_options* opt, cudaStream_t st);
 size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first);
+// the combination of score maps, the turn back of rotated values, the per-head norm, scale and gate (see b200_attn_finish)
+void launch_attn_finish(void* out, const float* a, const float* gate, int ld_gate, int gate_elems,
+                        const int64_t* positions, const double* v_rot_freq, int rot_half, int maps, float lambda,
+                        int head_norm, float eps, float out_scale, int T, int heads, int vdim, int dt, cudaStream_t st);
 
 void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const float* taps_w, const float* bias,
                             float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs,
                             int num_rows, int C, int taps, cudaStream_t st);
+// chan_decay (may be NULL): ready-made decays per head and key channel [T, heads, dim] (row stride ld_decay); with it
+// a_raw, a_log and dt_bias are not used
 void launch_delta_rule(float* out, const float* q, const float* k, const float* v, int ld, const float* b_raw,
-                       const float* a_raw, int ld_ba, const float* a_log, const float* dt_bias, float* state,
-                       const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads,
-                       int kv_heads, int dim, int vdim, cudaStream_t st);
+                       const float* a_raw, int ld_ba, const float* a_log, const float* dt_bias, const float* chan_decay,
+                       int ld_decay, float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx,
+                       int num_seqs, int heads, int kv_heads, int dim, int vdim, cudaStream_t st);
 void launch_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm, int ld, const float* dt_raw,
                      int ld_dt, const float* a_log, const float* dt_bias, const float* d_skip, float* state,
                      const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads, int groups,
                      int nstate, int vdim, cudaStream_t st);
 
-void launch_lowrank_decay(float* out, const float* low, int ld_low, const float* w2, const float* bias, float tau, int T,
-                          int C, int rank, cudaStream_t st);
+// a_log (may be NULL): the delta rule's decay exp(-exp(a_log[c / a_period]) softplus(z)) instead of sigmoid(z)^(1/tau)
+void launch_lowrank_decay(float* out, const float* low, int ld_low, const float* w2, const float* bias, float tau,
+                          const float* a_log, int a_period, int T, int C, int rank, cudaStream_t st);
 void launch_decay_attn(float* out, const float* q, const float* k, const float* v, int ld, const float* head_decay,
                        const float* chan_decay, int ld_decay, float q_scale, float k_scale, int act, float* state,
                        const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads, int dim,

@@ -17,6 +17,15 @@
 //   * in the prep kernel: q / k norms per head with one weight of size dim shared by the heads (instead of over the
 //     whole projection), values that are the un-normed key rows (no v projection), and a query temperature
 //     1 + coef * ln(floor((p + 1) / every) + 1) at position p
+//   * rotary pairs either interleaved (2i, 2i+1) or as the two halves of the rotated part (i, i + rot_dims / 2), with a
+//     factor on cos and sin
+//   * rotated values: the value row of position j is turned by j (all of vdim) before it is cached, and
+//     attn_finish_kernel turns a head's output back by its own position, so that a value enters the output turned by
+//     the distance between key and query
+//   * a chunked mask: position i sees j <= i only inside its own chunk of `chunk` positions (counted from position 0)
+//   * several score maps over one set of values (differential attention): the maps' query and key heads are laid out
+//     map after map, the value cache has v_heads heads and key head g reads value head g % v_heads; the maps' outputs
+//     are written in fp32 and attn_finish_kernel combines them (a_0 - lambda a_1), norms per head, scales and gates
 //
 // window_attn_prep_kernel: from the fused projection row [q (heads x dim) | k (kv_heads x dim) | v (kv_heads x vdim) | ...]
 // (fp32) it adds the projection biases, RMS-norms q and k over their WHOLE projection (all heads at once, weights of
@@ -43,15 +52,18 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
                                         const int64_t* __restrict__ slots, float* __restrict__ q_out,
                                         T* __restrict__ k_cache, T* __restrict__ v_cache, int heads, int kv_heads,
                                         int dim, int vdim, int rot_dims, float eps, int head_norm, int v_from_k,
-                                        int q_temp_every, float q_temp_coef) {
-  extern __shared__ float sm[];          // cos[rot_dims/2] | sin[rot_dims/2] | red[36] | hinv[heads + kv_heads]
-  const int half = rot_dims / 2;
+                                        int q_temp_every, float q_temp_coef, int rot_half, float rot_mag,
+                                        const double* __restrict__ v_rot_freq, int v_heads) {
+  extern __shared__ float sm[];          // cos[rot_dims/2] | sin[rot_dims/2] | red[36] | hinv[heads + kv_heads] | vcos, vsin[vdim/2]
+  const int half = rot_dims / 2, vhalf = vdim / 2;
   float* cs = sm;
   float* sn = sm + half;
   float* red = sm + 2 * half;
   float* hinv = red + 36;
+  float* vcs = hinv + heads + kv_heads;
+  float* vsn = vcs + vhalf;
   const int t = blockIdx.x;
-  const int nq = heads * dim, nk = kv_heads * dim, nv = kv_heads * vdim;
+  const int nq = heads * dim, nk = kv_heads * dim, nv = v_heads * vdim;
   const float* qr = proj + static_cast<size_t>(t) * ld;
   const float* kr = qr + nq;
   const float* vr = v_from_k ? kr : kr + nk;            // the value row is a copy of the raw key row (vdim == dim)
@@ -65,9 +77,16 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     double s, c;
     sincos(pos * rot_freq[i], &s, &c);
-    cs[i] = static_cast<float>(c);
-    sn[i] = static_cast<float>(s);
+    cs[i] = static_cast<float>(c) * rot_mag;
+    sn[i] = static_cast<float>(s) * rot_mag;
   }
+  if (v_rot_freq)
+    for (int i = threadIdx.x; i < vhalf; i += blockDim.x) {
+      double s, c;
+      sincos(pos * v_rot_freq[i], &s, &c);
+      vcs[i] = static_cast<float>(c);
+      vsn[i] = static_cast<float>(s);
+    }
   float inv_q = 1.f, inv_k = 1.f;
   if (head_norm) {                       // every q and k head on its own: a warp per head
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,27 +129,49 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
     };
     const int d = e % dim;
     if (d >= rot_dims) return plain(e);
-    const int i = d >> 1, e0 = e - (d & 1);
-    const float u = plain(e0), v = plain(e0 + 1);
-    return (d & 1) ? v * cs[i] + u * sn[i] : u * cs[i] - v * sn[i];
+    // the pair (u, v) this entry belongs to, and whether it is the pair's second member
+    const bool second = rot_half ? d >= half : (d & 1) != 0;
+    const int i = rot_half ? (second ? d - half : d) : d >> 1;
+    const int eu = rot_half ? e - d + i : e - (d & 1), ev = rot_half ? eu + half : eu + 1;
+    const float u = plain(eu), v = plain(ev);
+    return second ? v * cs[i] + u * sn[i] : u * cs[i] - v * sn[i];
   };
   for (int e = threadIdx.x; e < nq; e += blockDim.x)
     q_out[static_cast<size_t>(t) * nq + e] = entry(qr, bq, q_norm_w, inv_q, 0, e) * q_temp;
   const int64_t slot = slots[t];
-  if (slot >= 0) {
+  if (slot >= 0 && k_cache) {            // no cache: the row brought queries only
     for (int e = threadIdx.x; e < nk; e += blockDim.x)
       st(k_cache + static_cast<size_t>(slot) * nk + e, entry(kr, bk, k_norm_w, inv_k, heads, e));
-    for (int e = threadIdx.x; e < nv; e += blockDim.x)
-      st(v_cache + static_cast<size_t>(slot) * nv + e, vr[e] + (bv ? bv[e] : 0.f));
+    for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+      float val = vr[e] + (bv ? bv[e] : 0.f);
+      if (v_rot_freq) {                  // the value row turned by its own position, all of vdim
+        const int d = e % vdim;
+        const bool second = rot_half ? d >= vhalf : (d & 1) != 0;
+        const int i = rot_half ? (second ? d - vhalf : d) : d >> 1;
+        const int eo = second ? (rot_half ? e - vhalf : e - 1) : (rot_half ? e + vhalf : e + 1);   // the other member
+        const float other = vr[eo] + (bv ? bv[eo] : 0.f);
+        val = second ? val * vcs[i] + other * vsn[i] : val * vcs[i] - other * vsn[i];
+      }
+      st(v_cache + static_cast<size_t>(slot) * nv + e, val);
+    }
   }
 }
 
 // The keys that position `pos` sees, as one run of indices 0 .. count-1: first the kept tokens that have left the
 // window, then the window itself.
+// first position of the window (and, with a chunked mask, of the chunk) that position `pos` sees
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  return chunk > 0 ? max(lo, pos / chunk * chunk) : lo;
+}
+template <typename T> __device__ __forceinline__ void st_out(T* out, size_t i, float v, int f32) {
+  if (f32) reinterpret_cast<float*>(out)[i] = v;
+  else st(out + i, v);
+}
 struct Visible {
   int n_first, lo, count;
-  __device__ __forceinline__ Visible(int pos, int window, int keep_first) {
-    lo = window > 0 ? max(0, pos - window + 1) : 0;
+  __device__ __forceinline__ Visible(int pos, int window, int keep_first, int chunk = 0) {
+    lo = first_visible(pos, window, chunk);
     n_first = min(max(keep_first, 0), lo);
     count = n_first + (pos - lo + 1);
   }
@@ -149,7 +190,8 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
                                    int max_blocks, int num_seqs, int heads, int kv_heads, int dim, int vdim, int window,
                                    int keep_first, float scale, float softcap, int key_tile, int nsplit,
                                    float* __restrict__ part_o, float* __restrict__ part_ml,
-                                   const float* __restrict__ slopes, int gate_elems) {
+                                   const float* __restrict__ slopes, int gate_elems, int chunk, int v_heads,
+                                   int out_f32) {
   extern __shared__ float sm[];
   const int Dp = dim | 1;                               // odd row pitch: a lane per key reads conflict-free
   const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -161,8 +203,9 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
   const int b = seq_of_row(cu, num_seqs, t);
   const int qlen = static_cast<int>(cu[b + 1] - cu[b]);
   const int pos = static_cast<int>(ctx[b]) - qlen + (t - static_cast<int>(cu[b]));
-  const Visible vis(pos, window, keep_first);
+  const Visible vis(pos, window, keep_first, chunk);
   const int per_group = heads / kv_heads;
+  const int gv = g % v_heads;                           // the value head this key head reads
   const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
   const int ntiles = (vis.count + key_tile - 1) / key_tile;
   const int per = (ntiles + nsplit - 1) / nsplit;
@@ -195,7 +238,7 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
       for (int e = threadIdx.x; e < nk * vdim; e += blockDim.x) {
         const int k = e / vdim, d = e % vdim, j = vis.key(i0 + k);
         const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
-        vs[k * vdim + d] = ld(v_cache + (slot * kv_heads + g) * vdim + d);
+        vs[k * vdim + d] = ld(v_cache + (slot * v_heads + gv) * vdim + d);
       }
       __syncthreads();
       if (!live) continue;
@@ -232,8 +275,8 @@ __global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict_
       float inv = l > 0.f ? 1.f / l : 0.f;
       if (gate && !gate_elems) inv *= sigmoid_f(gate[static_cast<size_t>(t) * ld_gate + h]);
       const float* ge = (gate && gate_elems) ? gate + static_cast<size_t>(t) * ld_gate + static_cast<size_t>(h) * vdim : nullptr;
-      T* o = out + (static_cast<size_t>(t) * heads + h) * vdim;
-      for (int d = lane; d < vdim; d += 32) st(o + d, os[warp * vdim + d] * inv * (ge ? sigmoid_f(ge[d]) : 1.f));
+      const size_t o = (static_cast<size_t>(t) * heads + h) * vdim;
+      for (int d = lane; d < vdim; d += 32) st_out(out, o + d, os[warp * vdim + d] * inv * (ge ? sigmoid_f(ge[d]) : 1.f), out_f32);
     } else if (live) {
       const size_t pi = (static_cast<size_t>(t) * heads + h) * nsplit + blockIdx.z;
       for (int d = lane; d < vdim; d += 32) part_o[pi * vdim + d] = os[warp * vdim + d];
@@ -250,7 +293,7 @@ template <typename T>
 __global__ void window_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, const float* __restrict__ sink,
                                          const float* __restrict__ gate, int ld_gate, int heads, int vdim, int nsplit,
-                                         int gate_elems) {
+                                         int gate_elems, int out_f32) {
   const size_t th = blockIdx.x;
   const int h = static_cast<int>(th % heads);
   const size_t t = th / heads;
@@ -265,7 +308,7 @@ __global__ void window_attn_merge_kernel(T* __restrict__ out, const float* __res
   for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
     float acc = 0.f;
     for (int z = 0; z < nsplit; ++z) acc += part_o[(th * nsplit + z) * vdim + d] * expf(ml[2 * z] - m);
-    st(out + th * vdim + d, acc * inv * (ge ? sigmoid_f(ge[d]) : 1.f));
+    st_out(out, th * vdim + d, acc * inv * (ge ? sigmoid_f(ge[d]) : 1.f), out_f32);
   }
 }
 
@@ -277,20 +320,31 @@ void launch_window_attn_prep(const float* proj, int ld, const float* bias, const
   const int head_norm = opt ? opt->head_norm : 0, v_from_k = opt ? opt->v_from_k : 0;
   const int q_every = opt ? opt->q_temp_every : 0;
   const float q_coef = opt ? opt->q_temp_coef : 0.f;
-  if (v_from_k && vdim != dim) {
-    set_error(1, "window_attn_prep: values taken from the key rows need vdim == dim");
+  const int rot_half = opt ? opt->rot_half : 0;
+  const float rot_mag = (opt && opt->rot_mag != 0.f) ? opt->rot_mag : 1.f;
+  const double* v_rot = opt ? opt->v_rot_freq : nullptr;
+  const int v_heads = (opt && opt->v_heads > 0) ? opt->v_heads : kv_heads;
+  if (opt && opt->no_cache) k_cache = v_cache = nullptr;
+  if (v_from_k && (vdim != dim || v_heads != kv_heads)) {
+    set_error(1, "window_attn_prep: values taken from the key rows need vdim == dim and as many value heads as key heads");
     return;
   }
-  const size_t smem = (static_cast<size_t>(rot_dims) + 40 + heads + kv_heads) * 4;
+  if ((v_rot && (vdim % 2 != 0 || v_from_k)) || kv_heads % v_heads != 0) {
+    set_error(1, "window_attn_prep: rotated values need an even vdim and a projection of their own; kv_heads is a multiple of v_heads");
+    return;
+  }
+  const size_t smem = (static_cast<size_t>(rot_dims) + 40 + heads + kv_heads + vdim + 2) * 4;
   if (dt)
     window_attn_prep_kernel<float><<<T, 256, smem, st_>>>(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions, slots,
                                                           q_out, (float*)k_cache, (float*)v_cache, heads, kv_heads, dim,
-                                                          vdim, rot_dims, eps, head_norm, v_from_k, q_every, q_coef);
+                                                          vdim, rot_dims, eps, head_norm, v_from_k, q_every, q_coef,
+                                                          rot_half, rot_mag, v_rot, v_heads);
   else
     window_attn_prep_kernel<__nv_bfloat16><<<T, 256, smem, st_>>>(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions,
                                                                   slots, q_out, (__nv_bfloat16*)k_cache,
                                                                   (__nv_bfloat16*)v_cache, heads, kv_heads, dim, vdim,
-                                                                  rot_dims, eps, head_norm, v_from_k, q_every, q_coef);
+                                                                  rot_dims, eps, head_norm, v_from_k, q_every, q_coef,
+                                                                  rot_half, rot_mag, v_rot, v_heads);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -326,7 +380,7 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
                        const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_heads,
                        int dim, int vdim, int window, int keep_first, float scale, float softcap, int nsplit,
                        float* __restrict__ part_o, float* __restrict__ part_ml, const float* __restrict__ slopes,
-                       int gate_elems) {
+                       int gate_elems, int chunk, int v_heads, int out_f32) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int P = dim + 8, PV = vdim + 8;                   // row pitches in bf16 elements (16-byte multiples)
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [WKT][P]
@@ -362,7 +416,8 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
   }
   const int pos0 = static_cast<int>(ctx[b]) - static_cast<int>(cu[b + 1] - cu[b]) + (row0 - static_cast<int>(cu[b]));
   const int pos_last = HROWS ? pos0 : pos0 + nrows - 1;
-  const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;        // first key of the window of the first row
+  const int key_lo = first_visible(pos0, window, chunk);               // first key of the window of the first row
+  const int vh = kvh % v_heads;                                         // the value head this key head reads
   for (int e = threadIdx.x; e < WQ * dim; e += blockDim.x) {
     const int r = e / dim, d = e % dim;
     const size_t qrow = HROWS ? static_cast<size_t>(row0) * heads + h + r : static_cast<size_t>(row0 + r) * heads + h;
@@ -387,7 +442,7 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
   // [win_begin, pos_last] the window.  Head rows: tiles of the one token's visible keys, this block's run of them.
   const int win_begin = (key_lo / WKT) * WKT;
   const int kept_end = min(win_begin, ((min(max(keep_first, 0), key_lo) + WKT - 1) / WKT) * WKT);
-  const Visible vis(pos0, window, keep_first);
+  const Visible vis(pos0, window, keep_first, chunk);
   const int ntiles = (vis.count + WKT - 1) / WKT, per = (ntiles + nsplit - 1) / nsplit;
   const int t_first = HROWS ? static_cast<int>(blockIdx.z) * per * WKT : 0;
   const int t_end = HROWS ? min(vis.count, t_first + per * WKT) : pos_last + 1;       // exclusive
@@ -413,7 +468,7 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
       if (j0 + k < t_end) {
         const int j = tile_key(k);
         const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
-        v = *reinterpret_cast<const uint4*>(v_cache + (slot * kv_heads + kvh) * vdim + d);
+        v = *reinterpret_cast<const uint4*>(v_cache + (slot * v_heads + vh) * vdim + d);
       }
       *reinterpret_cast<uint4*>(Vs + static_cast<size_t>(k) * PV + d) = v;
     }
@@ -446,7 +501,7 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
       const int r = g + rr * 8;
-      const int lo = window > 0 ? max(0, rowp[rr] - window + 1) : 0;
+      const int lo = first_visible(rowp[rr], window, chunk);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
 #pragma unroll
@@ -519,8 +574,13 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
       for (int n = 0; n < NT; ++n) {
         const int d = (warp * NT + n) * 8 + 2 * tq;
         const float g0 = ge ? sigmoid_f(ge[d]) : 1.f, g1 = ge ? sigmoid_f(ge[d + 1]) : 1.f;
-        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv * g0, o[n][rr * 2 + 1] * inv * g1);
-        *reinterpret_cast<__nv_bfloat162*>(out + orow * vdim + d) = v;
+        if (out_f32) {
+          *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + orow * vdim + d) =
+              make_float2(o[n][rr * 2] * inv * g0, o[n][rr * 2 + 1] * inv * g1);
+        } else {
+          __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv * g0, o[n][rr * 2 + 1] * inv * g1);
+          *reinterpret_cast<__nv_bfloat162*>(out + orow * vdim + d) = v;
+        }
       }
     } else {
       const size_t pi = orow * nsplit + blockIdx.z;
@@ -555,7 +615,7 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
                         const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
                         const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_heads,
                         int dim, int vdim, int window, int keep_first, float scale, float softcap,
-                        const float* __restrict__ slopes, int gate_elems) {
+                        const float* __restrict__ slopes, int gate_elems, int chunk, int v_heads, int out_f32) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int P = dim + 8, PV = vdim + 8;
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [WKT][P]
@@ -578,11 +638,11 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
     }
     if (b < 0) return;
   }
-  const int h = blockIdx.y, kvh = h / (heads / kv_heads);
+  const int h = blockIdx.y, kvh = h / (heads / kv_heads), vh = kvh % v_heads;
   const float slope = slopes ? slopes[h] : 0.f;
   const int pos0 = static_cast<int>(ctx[b]) - static_cast<int>(cu[b + 1] - cu[b]) + (row0 - static_cast<int>(cu[b]));
   const int pos_last = pos0 + nrows - 1;
-  const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int key_lo = first_visible(pos0, window, chunk);
   for (int e = threadIdx.x; e < RQ * dim; e += blockDim.x) {
     const int r = e / dim, d = e % dim;
     const float v = r < nrows ? q[(static_cast<size_t>(row0 + r) * heads + h) * dim + d] : 0.f;
@@ -621,7 +681,7 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
       uint4 v = make_uint4(0, 0, 0, 0);
       if (j <= pos_last) {
         const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
-        v = *reinterpret_cast<const uint4*>(v_cache + (slot * kv_heads + kvh) * vdim + d);
+        v = *reinterpret_cast<const uint4*>(v_cache + (slot * v_heads + vh) * vdim + d);
       }
       *reinterpret_cast<uint4*>(Vs + static_cast<size_t>(k) * PV + d) = v;
     }
@@ -629,7 +689,7 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
     // this warp's rows see nothing of the tile: every key is later than its last row, or the tile lies wholly between
     // the kept tokens and the window of its first row
     const int w_first = pos0 + wr, w_last = min(pos0 + wr + 15, pos_last);
-    const int w_lo = window > 0 ? max(0, w_first - window + 1) : 0;
+    const int w_lo = first_visible(w_first, window, chunk);
     if (wr >= nrows || j0 > w_last || (j0 + WKT <= w_lo && j0 >= keep_first)) continue;
     float sc[8][4];
 #pragma unroll
@@ -656,7 +716,7 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
     float mx[2] = {-1e30f, -1e30f};
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
-      const int lo = window > 0 ? max(0, rowp[rr] - window + 1) : 0;
+      const int lo = first_visible(rowp[rr], window, chunk);
 #pragma unroll
       for (int n = 0; n < 8; ++n)
 #pragma unroll
@@ -726,8 +786,13 @@ window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict
     for (int n = 0; n < NTV; ++n) {
       const int d = n * 8 + 2 * tq;
       const float g0 = ge ? sigmoid_f(ge[d]) : 1.f, g1 = ge ? sigmoid_f(ge[d + 1]) : 1.f;
-      __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv * g0, o[n][rr * 2 + 1] * inv * g1);
-      *reinterpret_cast<__nv_bfloat162*>(out + (trow * heads + h) * vdim + d) = v;
+      if (out_f32) {
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(out) + (trow * heads + h) * vdim + d) =
+            make_float2(o[n][rr * 2] * inv * g0, o[n][rr * 2 + 1] * inv * g1);
+      } else {
+        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv * g0, o[n][rr * 2 + 1] * inv * g1);
+        *reinterpret_cast<__nv_bfloat162*>(out + (trow * heads + h) * vdim + d) = v;
+      }
     }
   }
 }
@@ -788,6 +853,12 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
   if (T <= 0) return;
   const float* slopes = opt ? opt->dist_slopes : nullptr;
   const int gate_elems = opt ? opt->gate_elems : 0;
+  const int chunk = opt ? opt->chunk : 0, out_f32 = opt ? opt->out_f32 : 0;
+  const int v_heads = (opt && opt->v_heads > 0) ? opt->v_heads : kv_heads;
+  if (kv_heads % v_heads != 0) {
+    set_error(1, "window_attn: kv_heads is a multiple of v_heads");
+    return;
+  }
   // bf16, steps of many rows, value sizes up to 128: the tensor-core form with 64 token rows per block
   if (!dt && window_mma_enabled() && T > 2 * sm_count() / 4 && window_rows_enabled() && dim % 16 == 0 && vdim % 16 == 0 &&
       vdim <= 128) {
@@ -800,7 +871,7 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
     kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,                          \
                                    (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,      \
                                    max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,    \
-                                   softcap, slopes, gate_elems);                                                   \
+                                   softcap, slopes, gate_elems, chunk, v_heads, out_f32);                          \
   }
     bool done = smem <= 200 * 1024;
     if (done) switch (vdim / 8) {
@@ -836,7 +907,7 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
     kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,                          \
                                    (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,      \
                                    max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,    \
-                                   softcap, nsplit, part_o, part_ml, slopes, gate_elems);                          \
+                                   softcap, nsplit, part_o, part_ml, slopes, gate_elems, chunk, v_heads, out_f32); \
   }
 #define B200_WMMA(NT)                 \
   if (hrows) B200_WMMA2(NT, true)     \
@@ -858,7 +929,8 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
       if (nsplit > 1) {
         const int th = vdim >= 256 ? 256 : (vdim >= 128 ? 128 : 64);
         window_attn_merge_kernel<__nv_bfloat16><<<T * heads, th, 0, st_>>>((__nv_bfloat16*)out, part_o, part_ml, sink,
-                                                                           gate, ld_gate, heads, vdim, nsplit, gate_elems);
+                                                                           gate, ld_gate, heads, vdim, nsplit, gate_elems,
+                                                                           out_f32);
         B200_CUDA_LAUNCH_CHECK();
       }
       return;
@@ -886,37 +958,121 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, nw * 32, smem, st_>>>((float*)out, q, (const float*)k_cache, (const float*)v_cache, sink, gate, ld_gate,
                                        cu, ctx, block_tables, max_blocks, num_seqs, heads, kv_heads, dim, vdim, window,
-                                       keep_first, scale, softcap, key_tile, nsplit, part_o, part_ml, slopes, gate_elems);
+                                       keep_first, scale, softcap, key_tile, nsplit, part_o, part_ml, slopes, gate_elems,
+                                       chunk, v_heads, out_f32);
   } else {
     auto kern = window_attn_kernel<__nv_bfloat16>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, nw * 32, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,
                                        (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,
                                        max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,
-                                       softcap, key_tile, nsplit, part_o, part_ml, slopes, gate_elems);
+                                       softcap, key_tile, nsplit, part_o, part_ml, slopes, gate_elems, chunk, v_heads,
+                                       out_f32);
   }
   B200_CUDA_LAUNCH_CHECK();
   if (nsplit > 1) {
     const int th = vdim >= 256 ? 256 : (vdim >= 128 ? 128 : 64);
     if (dt)
       window_attn_merge_kernel<float><<<T * heads, th, 0, st_>>>((float*)out, part_o, part_ml, sink, gate, ld_gate,
-                                                                 heads, vdim, nsplit, gate_elems);
+                                                                 heads, vdim, nsplit, gate_elems, out_f32);
     else
       window_attn_merge_kernel<__nv_bfloat16><<<T * heads, th, 0, st_>>>((__nv_bfloat16*)out, part_o, part_ml, sink,
-                                                                         gate, ld_gate, heads, vdim, nsplit, gate_elems);
+                                                                         gate, ld_gate, heads, vdim, nsplit, gate_elems,
+                                                                         out_f32);
     B200_CUDA_LAUNCH_CHECK();
   }
+}
+
+// One block per token, a warp per head at a time: what follows the softmax-weighted sums where more than a gate does.
+//   o = a[map 0] - lambda * a[map 1]                (maps == 2; the maps lie one after the other: a [T, maps, heads, vdim])
+//   o turned back by -position * v_rot_freq[m]      (rotated values; cos / sin of the token's angles in shared memory,
+//                                                    angles in double as where the values were turned)
+//   o / sqrt(mean(o^2) + eps) per head, no weight   (head_norm)
+//   o * out_scale * sigmoid(gate)                   (gate per head or per element)
+template <typename T>
+__global__ void attn_finish_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ gate,
+                                   int ld_gate, int gate_elems, const int64_t* __restrict__ positions,
+                                   const double* __restrict__ v_rot_freq, int rot_half, int maps, float lambda,
+                                   int head_norm, float eps, float out_scale, int heads, int vdim) {
+  extern __shared__ float sm[];          // cos[vdim/2] | sin[vdim/2]
+  const int vhalf = vdim / 2;
+  float* cs = sm;
+  float* sn = sm + vhalf;
+  const int t = blockIdx.x, nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (v_rot_freq) {
+    const double pos = static_cast<double>(positions[t]);
+    for (int i = threadIdx.x; i < vhalf; i += blockDim.x) {
+      double s, c;
+      sincos(pos * v_rot_freq[i], &s, &c);
+      cs[i] = static_cast<float>(c);
+      sn[i] = static_cast<float>(s);
+    }
+    __syncthreads();
+  }
+  const size_t map_stride = static_cast<size_t>(heads) * vdim;
+  for (int h = warp; h < heads; h += nw) {
+    const float* a0 = a + (static_cast<size_t>(t) * maps * heads + h) * vdim;
+    auto val = [&](int d) { return maps == 2 ? a0[d] - lambda * a0[map_stride + d] : a0[d]; };
+    float inv = out_scale;
+    if (head_norm) {
+      float ss = 0.f;
+      for (int d = lane; d < vdim; d += 32) ss += val(d) * val(d);
+      ss = lanes_sum(ss);
+      inv *= 1.f / sqrtf(ss / static_cast<float>(vdim) + eps);
+    }
+    if (gate && !gate_elems) inv *= sigmoid_f(gate[static_cast<size_t>(t) * ld_gate + h]);
+    const float* ge = (gate && gate_elems) ? gate + static_cast<size_t>(t) * ld_gate + static_cast<size_t>(h) * vdim : nullptr;
+    T* o = out + (static_cast<size_t>(t) * heads + h) * vdim;
+    for (int d = lane; d < vdim; d += 32) {
+      float v = val(d);
+      if (v_rot_freq) {                  // the inverse turn: (u, w) -> (u cos + w sin, w cos - u sin)
+        const bool second = rot_half ? d >= vhalf : (d & 1) != 0;
+        const int i = rot_half ? (second ? d - vhalf : d) : d >> 1;
+        const float other = val(second ? (rot_half ? d - vhalf : d - 1) : (rot_half ? d + vhalf : d + 1));
+        v = second ? v * cs[i] - other * sn[i] : v * cs[i] + other * sn[i];
+      }
+      st(o + d, v * inv * (ge ? sigmoid_f(ge[d]) : 1.f));
+    }
+  }
+}
+
+void launch_attn_finish(void* out, const float* a, const float* gate, int ld_gate, int gate_elems,
+                        const int64_t* positions, const double* v_rot_freq, int rot_half, int maps, float lambda,
+                        int head_norm, float eps, float out_scale, int T, int heads, int vdim, int dt, cudaStream_t st_) {
+  if (T <= 0) return;
+  if (maps < 1 || maps > 2 || (v_rot_freq && (vdim % 2 != 0 || !positions))) {
+    set_error(1, "attn_finish: one or two score maps; turning values back needs an even vdim and the positions");
+    return;
+  }
+  const int threads = heads >= 8 ? 256 : (heads >= 4 ? 128 : 64);
+  const size_t smem = static_cast<size_t>(vdim + 2) * 4;
+  if (dt)
+    attn_finish_kernel<float><<<T, threads, smem, st_>>>((float*)out, a, gate, ld_gate, gate_elems, positions, v_rot_freq,
+                                                         rot_half, maps, lambda, head_norm, eps, out_scale, heads, vdim);
+  else
+    attn_finish_kernel<__nv_bfloat16><<<T, threads, smem, st_>>>((__nv_bfloat16*)out, a, gate, ld_gate, gate_elems, positions,
+                                                                 v_rot_freq, rot_half, maps, lambda, head_norm, eps,
+                                                                 out_scale, heads, vdim);
+  B200_CUDA_LAUNCH_CHECK();
 }
 
 }  // namespace b200
 
 extern "C" {
+void b200_attn_finish(void* out, const float* a, const float* gate, int32_t ld_gate, int32_t gate_elems,
+                      const int64_t* positions, const double* v_rot_freq, int32_t rot_half, int32_t maps, float lambda,
+                      int32_t head_norm, float eps, float out_scale, int32_t num_tokens, int32_t heads, int32_t vdim,
+                      int32_t dt, int64_t stream) {
+  B200_CHECK_ARG(out && a && heads > 0 && vdim > 0 && (dt == 0 || dt == 1), "attn_finish: bad arguments");
+  b200::launch_attn_finish(out, a, gate, ld_gate, gate_elems, positions, v_rot_freq, rot_half, maps, lambda, head_norm,
+                           eps, out_scale, num_tokens, heads, vdim, dt, reinterpret_cast<cudaStream_t>(stream));
+}
 void b200_window_attn_prep_ex(const float* proj, int32_t ld, const float* bias, const float* q_norm_w,
                               const float* k_norm_w, const double* rot_freq, const int64_t* positions,
                               const int64_t* slot_mapping, float* q_out, void* k_cache, void* v_cache,
                               int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim,
                               int32_t rot_dims, float eps, int32_t dt, const b200_attn_options* opt, int64_t stream) {
-  B200_CHECK_ARG(proj && positions && slot_mapping && q_out && k_cache && v_cache && heads > 0 && kv_heads > 0 &&
+  B200_CHECK_ARG(proj && positions && slot_mapping && q_out && ((k_cache && v_cache) || (opt && opt->no_cache)) && heads > 0 && kv_heads > 0 &&
                      heads % kv_heads == 0 && dim > 0 && vdim > 0 && rot_dims >= 0 && rot_dims <= dim &&
                      rot_dims % 2 == 0 && (rot_dims == 0 || rot_freq) && (dt == 0 || dt == 1),
                  "window_attn_prep: bad arguments");

@@ -1,8 +1,9 @@
 """Runner of hybrid decoders with an fp32 residual stream over the C++ launch plan (b200_hybrid_*,
 csrc/host/hybrid_runner.cpp): the sibling of engine.ModelRunner for models whose layers choose between latent
 attention, windowed softmax attention, the gated delta rule, the SSD scan and decayed linear attention (one mixer, or
-two side by side), with a routed mixture of experts or a dense gated feed-forward, in a parallel, a sandwich
-(norm before and after each sublayer) or a post-norm (sublayer results normed on their way into the stream) layout.
+two side by side), with a routed mixture of experts or a dense feed-forward, in a parallel, a sandwich
+(norm before and after each sublayer), a post-norm (sublayer results normed on their way into the stream) or a
+pre-norm layout (RMS or dynamic-tanh norms, optional token shift and depth-weighted average of the layers' results).
 
 This module holds no model arithmetic.  It allocates what the C side borrows -- the paged latent caches, the
 paged K / V caches, the slot-indexed recurrent state pools, the workspace, pinned staging -- describes the layers to it, and moves a step's
@@ -20,7 +21,8 @@ from . import _lib
 from ._lib import HybridConfig, HybridLayer
 
 MIXER_LATENT_ATTN, MIXER_DELTA_RULE, MIXER_SSD, MIXER_WINDOW_ATTN, MIXER_DECAY_ATTN = 0, 1, 2, 3, 4
-LAYOUT_PARALLEL, LAYOUT_SANDWICH, LAYOUT_POSTNORM = 0, 1, 2
+LAYOUT_PARALLEL, LAYOUT_SANDWICH, LAYOUT_POSTNORM, LAYOUT_PRENORM = 0, 1, 2, 3
+NORM_RMS, NORM_DYNTANH = 0, 1
 PAGE = 64
 
 
@@ -32,13 +34,14 @@ class LayerSpec:
     dims: dict
     tensors: dict = field(default_factory=dict)
     side: "LayerSpec | None" = None      # a second mixer beside the first (reads the same norm; outputs are summed)
-    cache_from: "int | None" = None      # latent attention: read layer cache_from's latent cache (no cache of its own)
+    cache_from: "int | None" = None      # latent / window attention: read layer cache_from's cache (no cache of its own)
 
 
 class HybridRunner:
     def __init__(self, *, width, vocab, layers: list[LayerSpec], embed, final_norm, lm_head, norm_eps,
                  norm_weight_offset=0.0, embed_scale=1.0, embed_pos_base=0.0, dtype=torch.bfloat16, num_blocks, max_blocks_per_seq, max_seqs, max_tokens,
-                 num_state_slots, device="cuda", layer_trace=False):
+                 num_state_slots, device="cuda", layer_trace=False, final_norm_kind=NORM_RMS, final_norm_bias=None,
+                 final_norm_alpha=1.0):
         if dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("hybrid decoders run with bfloat16 or float32 operands")
         self._l = _lib.lib()
@@ -48,11 +51,11 @@ class HybridRunner:
                                 block_size=PAGE, num_blocks=num_blocks, max_blocks_per_seq=max_blocks_per_seq,
                                 max_seqs=max_seqs, max_tokens=max_tokens, num_state_slots=num_state_slots,
                                 norm_eps=norm_eps, norm_weight_offset=norm_weight_offset, embed_scale=embed_scale,
-                                embed_pos_base=embed_pos_base)
+                                embed_pos_base=embed_pos_base, final_norm_kind=final_norm_kind)
         self._h = self._l.b200_hybrid_new(C.byref(self.cfg))
         _lib.check()
-        self._keep = [embed, final_norm, lm_head]
-        self.kv_cache, self.v_cache, self.conv_state, self.rec_state = {}, {}, {}, {}
+        self._keep = [embed, final_norm, lm_head, final_norm_bias]
+        self.kv_cache, self.v_cache, self.conv_state, self.rec_state, self.shift_state = {}, {}, {}, {}, {}
         f32 = dict(dtype=torch.float32, device=self.device)
 
         def describe(key, spec):
@@ -71,8 +74,20 @@ class HybridRunner:
                 self.kv_cache[key] = torch.zeros(num_blocks, PAGE, d["kv_rank"] + d["rot_dim"], dtype=dtype,
                                                  device=self.device)
                 t["kv_cache"] = self.kv_cache[key]
+            elif spec.mixer == MIXER_WINDOW_ATTN and spec.cache_from is not None:
+                src = spec.cache_from
+                same = ("kv_heads", "dim", "vdim", "score_maps")
+                if not (isinstance(key, int) and 0 <= src < key and layers[src].mixer == MIXER_WINDOW_ATTN and
+                        layers[src].cache_from is None and
+                        all(layers[src].dims.get(n, 0) == d.get(n, 0) for n in same)):
+                    raise ValueError(f"layer {key}: shared K / V pages come from an earlier attention layer of the same "
+                                     "head counts and sizes that writes its own")
+                t["kv_cache"], t["v_cache"] = self.kv_cache[src], self.v_cache[src]
+                d = {**d, "shared_cache": 1}
             elif spec.mixer == MIXER_WINDOW_ATTN:
-                self.kv_cache[key] = torch.zeros(num_blocks, PAGE, d["kv_heads"], d["dim"], dtype=dtype, device=self.device)
+                maps = max(int(d.get("score_maps", 0)), 1)      # the maps' key heads lie one map after the other
+                self.kv_cache[key] = torch.zeros(num_blocks, PAGE, maps * d["kv_heads"], d["dim"], dtype=dtype,
+                                                 device=self.device)
                 self.v_cache[key] = torch.zeros(num_blocks, PAGE, d["kv_heads"], d["vdim"], dtype=dtype, device=self.device)
                 t["kv_cache"], t["v_cache"] = self.kv_cache[key], self.v_cache[key]
             elif spec.mixer == MIXER_DECAY_ATTN:
@@ -89,7 +104,10 @@ class HybridRunner:
                 self.conv_state[key] = torch.zeros(num_state_slots, max(taps - 1, 1), nconv, **f32)
                 self.rec_state[key] = torch.zeros(num_state_slots, d["heads"], rows, d["vdim"], **f32)
                 t["conv_state"], t["rec_state"] = self.conv_state[key], self.rec_state[key]
-            lw = HybridLayer(mixer=spec.mixer, **{"out_scale": 1.0, "q_scale": 1.0, "k_scale": 1.0, **d})
+            if t.get("shift_w") is not None:     # the previous token's normed row, per sequence
+                self.shift_state[key] = torch.zeros(num_state_slots, width, **f32)
+                t["shift_state"] = self.shift_state[key]
+            lw = HybridLayer(mixer=spec.mixer, **{"out_scale": 1.0, "q_scale": 1.0, "k_scale": 1.0, "ff_scale": 1.0, **d})
             for name, ten in t.items():
                 if ten is None:
                     continue
@@ -106,6 +124,9 @@ class HybridRunner:
                 self._l.b200_hybrid_set_layer_side(self._h, i, C.byref(describe((i, "side"), spec.side)))
                 _lib.check()
         self._l.b200_hybrid_set_globals(self._h, embed.data_ptr(), final_norm.data_ptr(), lm_head.data_ptr())
+        if final_norm_kind != NORM_RMS:
+            self._l.b200_hybrid_set_final_norm(self._h, 0 if final_norm_bias is None else final_norm_bias.data_ptr(),
+                                               float(final_norm_alpha))
         nbytes = self._l.b200_hybrid_workspace_bytes(self._h)
         self.workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         self._l.b200_hybrid_set_workspace(self._h, self.workspace.data_ptr(), nbytes)

@@ -29,7 +29,7 @@ def architecture_of(cfg: dict) -> str:
 
 
 # architectures served by hybrid.HybridRunner (the `hybrid` build target is all they need)
-HYBRID_ARCHITECTURES = ("Fidasun", "Zalalix", "Gibevik")
+HYBRID_ARCHITECTURES = ("Fidasun", "Zalalix", "Gibevik", "Tasadra")
 
 
 def registered() -> list[str]:
@@ -38,7 +38,7 @@ def registered() -> list[str]:
 
 
 def _load_builtin():
-    from . import fidasun, gibevik, llama, zalalix  # noqa: F401  (importing registers them)
+    from . import fidasun, gibevik, llama, tasadra, zalalix  # noqa: F401  (importing registers them)
 
 
 def build_runner(cfg: dict, tensors: dict, **kw):
