@@ -1,0 +1,557 @@
+"""Tasadra on the GPU against the plain restatement in tests/tasadra_ref.py: each mechanism alone (as a kernel and as a
+one-layer model), whole prompts against token-by-token decoding, portions down to two tokens, unequal batches against
+each request alone, pages and slots that are used again, keys far back, at page borders and just inside / just outside
+a chunk of the chunked mask (inputs made so that one key stands out), the first tokens of a sequence, long decoding,
+several sizes (also sizes of one), and greedy generation through LLMEngine.  fp32 runs are held to 2e-4 of the logits'
+spread, bf16 runs to 6e-2."""
+import json
+import math
+import struct
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import tasadra_ref as R
+from fidasun_util import Driver, rel_err
+from tasadra_util import full_cfg, layer, make_cfg, random_layers, random_tensors
+from zalalix_util import random_schedule
+
+pytestmark = pytest.mark.gpu
+F32_TOL, BF16_TOL = 2e-4, 6e-2
+D64 = torch.float64
+
+
+def ref_logits(cfg, tensors, tokens):
+    return R.forward(cfg, tensors, tokens).numpy()
+
+
+def toks(n, vocab, seed):
+    return np.random.default_rng(seed).integers(0, vocab, size=n).tolist()
+
+
+def _i32(a):
+    return torch.tensor(a, dtype=torch.int32, device="cuda")
+
+
+def tol_of(dtype):
+    return F32_TOL if dtype == torch.float32 else BF16_TOL
+
+
+# ------------------------------------------------------------------ the row kernels alone
+@pytest.mark.parametrize("kind", ["dyntanh", "rms"])
+def test_norm_with_token_shift_op(lib, kind):
+    """Two steps over three sequences: portions of 1, 2 and 70 rows, a sequence that starts at position 0 in a slot that
+    held another sequence's row (it must see zeros), one that goes on from its stored row, one that is left out of the
+    second step and whose stored row must survive it."""
+    from vllm_rs_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    D, slots = 40, 4
+    w, b, s = torch.randn(D, generator=g), torch.randn(D, generator=g), torch.rand(D, generator=g)
+    alpha, eps = 0.7, 1e-3
+    state = torch.randn(slots, D, generator=g).cuda()                 # rubbish a new sequence must not read
+    before = state.clone()
+
+    def plain(x):
+        x = x.double()
+        if kind == "dyntanh":
+            return R.dyn_tanh(x, w.double(), b.double(), alpha)
+        return R.unit_rms(x, eps) * w.double()
+
+    bias = b.cuda() if kind == "dyntanh" else None
+    x1 = torch.randn(73, D, generator=g)
+    lens1, slot1 = [70, 1, 2], [2, 0, 3]                               # all three start here
+    out = ops.stream_norm(x1.cuda(), w.cuda(), bias, kind=kind, alpha=alpha, eps=eps, shift_w=s.cuda(), shift_state=state,
+                          state_slots=_i32(slot1), cu_seqlens_q=_i32([0, 70, 71, 73]), context_lens=_i32(lens1)).cpu()
+    at, last = 0, {}
+    for n, sl in zip(lens1, slot1):
+        h = plain(x1[at:at + n])
+        assert torch.allclose(out[at:at + n].double(), R.token_shift(h, s.double()), atol=2e-5), sl
+        last[sl] = h[-1]
+        at += n
+    assert torch.equal(state[1], before[1])
+    for sl, row in last.items():
+        assert torch.allclose(state[sl].cpu().double(), row, atol=2e-5)
+    x2 = torch.randn(5, D, generator=g)                               # slot 2 goes on (1 row), slot 3 goes on (2), slot 1 is new (2)
+    out = ops.stream_norm(x2.cuda(), w.cuda(), bias, kind=kind, alpha=alpha, eps=eps, shift_w=s.cuda(), shift_state=state,
+                          state_slots=_i32([2, 3, 1]), cu_seqlens_q=_i32([0, 1, 3, 5]), context_lens=_i32([71, 4, 2])).cpu()
+    for (lo, hi), sl in (((0, 1), 2), ((1, 3), 3), ((3, 5), 1)):
+        h = plain(x2[lo:hi])
+        want = R.token_shift(h, s.double(), last.get(sl))             # slot 1: a new sequence, zeros
+        assert torch.allclose(out[lo:hi].double(), want, atol=2e-5), sl
+    assert torch.allclose(state[0].cpu().double(), last[0], atol=2e-5)      # left out of the step: untouched
+    plain_only = ops.stream_norm(x2.cuda(), w.cuda(), bias, kind=kind, alpha=alpha, eps=eps).cpu()
+    assert torch.allclose(plain_only.double(), plain(x2), atol=2e-5)
+
+
+def test_depth_mix_op(lib):
+    from vllm_rs_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    for shape in ((5, 7, 12), (2, 3, 33), (1, 9, 8)):
+        hist, w = torch.randn(*shape, generator=g), torch.randn(shape[0], generator=g)
+        out = ops.depth_mix(hist.cuda(), w.cuda()).cpu()
+        assert torch.allclose(out.double(), R.depth_average(list(hist.double()), w.double()), atol=1e-5)
+
+
+def test_attention_prep_rotations(lib):
+    """Per-head norms, the two-halves rotary layout on part of each head with scaled frequencies and a factor on cos and
+    sin, and value rows turned by their position over all of vdim, at positions up to 5000."""
+    from vllm_rs_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    H, G, dk, dv, n = 6, 2, 20, 14, 12
+    scaling = {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}
+    f, fac = R.pair_frequencies(n, 300.0, scaling)
+    fplain = R.pair_frequencies(n, 300.0)[0]
+    assert fac > 1.0 and (f < fplain).any() and (f == fplain).any()          # some pairs are slowed, some are not
+    fv = R.pair_frequencies(dv, 300.0)[0]
+    pos = torch.tensor([0, 1, 63, 64, 5000, 17])
+    T = len(pos)
+    slots = torch.tensor([3, 64, 2, 0, 130, 191])
+    proj = torch.randn(T, H * dk + G * dk + G * dv + H, generator=g) * 2        # gate logits ride along, untouched
+    qn, kn = torch.randn(dk, generator=g), torch.randn(dk, generator=g)
+    kc, vc = torch.zeros(3, 64, G, dk, device="cuda"), torch.zeros(3, 64, G, dv, device="cuda")
+    q = ops.window_attn_prep(proj.cuda(), None, qn.cuda(), kn.cuda(), f.cuda(), pos.cuda(), slots.cuda(), kc, vc, heads=H,
+                             rot_dims=n, eps=1e-4, head_norm=True, rot_half=True, rot_mag=fac, v_rot_freq=fv.cuda()).cpu()
+    x = proj.double()
+    ang, angv = pos[:, None].double() * f[None], pos[:, None].double() * fv[None]
+
+    def turned(rows, w):
+        rows = R.unit_rms(rows, 1e-4) * w.double()
+        return torch.cat([R.turn_halves(rows[..., :n], ang, fac), rows[..., n:]], -1)
+
+    assert torch.allclose(q.double(), turned(x[:, :H * dk].view(T, H, dk), qn), atol=3e-5)
+    wk = turned(x[:, H * dk:(H + G) * dk].view(T, G, dk), kn)
+    wv = R.turn_halves(x[:, (H + G) * dk:(H + G) * dk + G * dv].view(T, G, dv), angv)
+    for t in range(T):
+        s = int(slots[t])
+        assert torch.allclose(kc.cpu()[s // 64, s % 64].double(), wk[t], atol=3e-5), t
+        assert torch.allclose(vc.cpu()[s // 64, s % 64].double(), wv[t], atol=3e-5), t
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finish_op(lib, dtype):
+    """Turning back by the query's position undoes a turn by the same position; two maps are combined, normed per head,
+    scaled and gated per element."""
+    from vllm_rs_b200 import ops
+    g = torch.Generator().manual_seed(4)
+    T, H, dv = 9, 5, 12
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    pos = torch.tensor([0, 1, 2, 63, 64, 65, 1000, 4097, 7])
+    fv = R.pair_frequencies(dv, 50.0)[0]
+    o = torch.randn(T, H, dv, generator=g)
+    a = R.turn_halves(o.double(), pos[:, None].double() * fv[None]).float()
+    gate = torch.randn(T, H, generator=g)
+    out = ops.attn_finish(a.cuda(), gate.cuda(), pos.cuda(), heads=H, v_rot_freq=fv.cuda(), dtype=dtype).float().cpu()
+    assert (out.double() - o.double() * torch.sigmoid(gate.double())[:, :, None]).abs().max() <= tol * 4
+    a2 = torch.randn(T, 2 * H, dv, generator=g)
+    gate = torch.randn(T, H * dv, generator=g)
+    lam, eps, sc = 0.83, 1e-3, 0.4
+    out = ops.attn_finish(a2.cuda(), gate.cuda(), None, heads=H, maps=2, lam=lam, head_norm=True, eps=eps, out_scale=sc,
+                          dtype=dtype).float().cpu()
+    d = a2[:, :H].double() - lam * a2[:, H:].double()
+    want = R.unit_rms(d, eps) * sc * torch.sigmoid(gate.double()).view(T, H, dv)
+    assert (out.double() - want).abs().max() <= tol * 4
+
+
+def _plain_attention(q, k, v, rows_pos, scale, chunk, key_of, val_of):
+    """q [T, heads, dk] at positions rows_pos; k [n, key heads, dk], v [n, value heads, dv]; head h reads key head
+    key_of(h) and value head val_of(h); with chunk > 0 only keys of the query's own chunk are visible."""
+    H, n = q.shape[1], k.shape[0]
+    kk, vv = k[:, [key_of(h) for h in range(H)]], v[:, [val_of(h) for h in range(H)]]
+    pos, j = torch.tensor(rows_pos), torch.arange(n)
+    lo = pos // chunk * chunk if chunk else torch.zeros_like(pos)
+    see = (j[None, :] <= pos[:, None]) & (j[None, :] >= lo[:, None])
+    w = R.softmax_rows(torch.einsum("thd,nhd->thn", q, kk) * scale, see[:, None, :])
+    return torch.einsum("thn,nhd->thd", w, vv)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("split", [True, False])
+@pytest.mark.parametrize("dk,dv,H,G,maps", [(12, 10, 4, 2, 1), (32, 32, 3, 1, 2), (16, 64, 4, 2, 2), (16, 16, 34, 2, 1)])
+def test_chunked_attention_op_edges(lib, dtype, split, dk, dv, H, G, maps):
+    """Keys carry a position tag u and its square, so a query can put a sharp peak on any position.  Queries per row: a
+    peak on the first key of the row's chunk (just inside), on the key before it (just outside: had the kernel seen it,
+    it would take most of the weight), on the row's own position, on the next position (not yet visible) and on position
+    0 (hundreds of places back: visible only without chunks).  Chunks of 37 (edges inside pages), 64 (edges at page borders), 1 (a
+    key sees itself only) and none; prompt rows and single decoded rows on a shuffled block table; one or
+    two score maps over one set of values, the maps' heads laid out map after map."""
+    from vllm_rs_b200 import ops
+    n = 330
+    pages = [5, 2, 7, 0, 3, 6]
+    g = torch.Generator().manual_seed(0)
+    u = (torch.arange(n) - 160.0) / 256.0
+    k = torch.randn(n, maps * G, dk, generator=g) * 0.05
+    k[:, :, 0], k[:, :, 1] = u[:, None], (u * u)[:, None]
+    v = torch.randn(n, G, dv, generator=g)
+    kc = torch.zeros(8, 64, maps * G, dk, dtype=dtype, device="cuda")
+    vc = torch.zeros(8, 64, G, dv, dtype=dtype, device="cuda")
+    for j in range(n):
+        kc[pages[j // 64], j % 64], vc[pages[j // 64], j % 64] = k[j].to(dtype).cuda(), v[j].to(dtype).cuda()
+    kr, vr = k.to(dtype).double(), v.to(dtype).double()
+    bt = _i32([pages])
+    tol = 3e-3 if dtype == torch.float32 else 4e-2
+    sharp = 16384.0
+    per = H // G
+    key_of = lambda h: h // per                                   # noqa: E731  (heads of map m are h = m H .. m H + H - 1)
+    val_of = lambda h: (h // per) % G                             # noqa: E731
+    for chunk in (37, 64, 1, 0):
+        for rows_pos in ([329], [128], [64], [37], [0], list(range(200, 329)), list(range(0, 70)), list(range(100, 140))):
+            T = len(rows_pos)
+            pos = torch.tensor(rows_pos, dtype=torch.float32)
+            start = torch.floor(pos / chunk) * chunk if chunk else torch.zeros(T)
+            for form in ("inside", "outside", "self", "next", "first"):
+                target = {"inside": start, "outside": (start - 1).clamp(min=0), "self": pos, "next": pos + 1,
+                          "first": torch.zeros(T)}[form]
+                q = torch.randn(T, maps * H, dk, generator=g) * 0.1
+                ut = (target - 160.0) / 256.0
+                q[:, :, 0], q[:, :, 1] = (2.0 * sharp * ut)[:, None], -sharp
+                q = q.to(dtype).float()
+                out = ops.window_attn(q.cuda().contiguous(), kc, vc, None, None, _i32([0, T]), _i32([rows_pos[-1] + 1]),
+                                      bt, window=0, keep_first=0, scale=1.0, split=split, chunk=chunk,
+                                      out_f32=maps > 1).float().cpu()
+                want = _plain_attention(q.double(), kr, vr, rows_pos, 1.0, chunk, key_of, val_of)
+                assert (out.double() - want).abs().max() <= tol * max(1.0, want.abs().max().item()), (chunk, rows_pos[0], T, form)
+
+
+@pytest.mark.parametrize("H,G,dk,dv,rank", [(4, 2, 24, 40, 6), (2, 2, 16, 8, 1), (3, 1, 64, 24, 20), (1, 1, 130, 16, 4)])
+def test_channel_decay_and_delta_rule_ops(lib, H, G, dk, dv, rank):
+    """The decay per head and key channel from its low-rank projection, and the delta rule with it, over 300 tokens in
+    two steps (the state is carried in its slot); one head's decay is exactly one (its first write must still be read at
+    the end), and a second sequence starts in a slot that held rubbish."""
+    from vllm_rs_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    T = 300
+    low = torch.randn(T, rank, generator=g)
+    w2 = torch.randn(H * dk, rank, generator=g) * 0.5
+    bias = torch.randn(H * dk, generator=g) - 1.0
+    a_log = torch.randn(H, generator=g) * 0.5 - 0.5
+    w2[:dk], bias[:dk] = 0.0, -200.0                                  # head 0: softplus(-200) = 0, the decay is one
+    decay = ops.channel_decay(low.cuda(), w2.cuda(), bias.cuda(), a_log.cuda(), dk).cpu()
+    z = low.double() @ w2.double().T + bias.double()
+    want = torch.exp(-torch.exp(a_log.double()).repeat_interleave(dk)[None] * torch.nn.functional.softplus(z))
+    assert torch.allclose(decay.double(), want, atol=2e-6) and (decay[:, :dk] == 1.0).all()
+    q, k = torch.randn(T, G, dk, generator=g), torch.randn(T, G, dk, generator=g)
+    v, b_raw = torch.randn(T, H, dv, generator=g), torch.randn(T, H, generator=g)
+    state = torch.randn(3, H, dk, dv, generator=g).cuda()
+    outs = []
+    for lo, hi in ((0, 130), (130, T)):
+        outs.append(ops.delta_rule_chan(q[lo:hi].cuda(), k[lo:hi].cuda(), v[lo:hi].cuda(), b_raw[lo:hi].cuda(),
+                                        decay[lo:hi].cuda(), state, _i32([1]), _i32([0, hi - lo]), _i32([hi])).cpu())
+    got = torch.cat(outs, 0).double()
+    qn = q.double() / torch.sqrt((q.double() ** 2).sum(-1, keepdim=True) + 1e-6) / math.sqrt(dk)
+    kn = k.double() / torch.sqrt((k.double() ** 2).sum(-1, keepdim=True) + 1e-6)
+    qn, kn = qn.repeat_interleave(H // G, 1), kn.repeat_interleave(H // G, 1)
+    beta, gd = torch.sigmoid(b_raw.double()), want.view(T, H, dk)
+    S = torch.zeros(H, dk, dv, dtype=D64)
+    for t in range(T):
+        S = gd[t][:, :, None] * S
+        uu = beta[t][:, None] * (v[t].double() - torch.einsum("hkv,hk->hv", S, kn[t]))
+        S = S + kn[t][:, :, None] * uu[:, None, :]
+        assert (got[t] - torch.einsum("hkv,hk->hv", S, qn[t])).abs().max() <= 2e-4, t
+    assert torch.allclose(state[1].cpu().double(), S, atol=2e-4)
+
+
+# ------------------------------------------------------------------ each mixer alone (one-layer models)
+@pytest.mark.parametrize("kind,ff,kw", [
+    ("attention", 0, {}),
+    ("attention", 40, dict(heads=5, kv_heads=5, dim=24, vdim=24, softcap=0.0, rot={"base": 100.0, "dims": 24})),
+    ("attention", 0, dict(heads=3, kv_heads=1, dim=32, vdim=64)),                               # tensor-core forms
+    ("attention", 0, dict(heads=34, kv_heads=2, dim=16, vdim=32, rot={"base": 10000.0, "dims": 2})),   # a group wider than an MMA tile
+    ("channel_delta", 0, {}),
+    ("channel_delta", 24, dict(heads=1, kv_heads=1, dim=2, vdim=2, conv=1, a_rank=1, g_rank=1)),
+    ("channel_delta", 0, dict(heads=6, kv_heads=2, dim=64, vdim=48, conv=4, a_rank=16, g_rank=24)),
+    ("attention_2", 0, {}),
+    ("attention_2", 40, dict(heads=2, kv_heads=2, dim=16, vdim=32, mask={"size": 64})),         # tensor-core forms
+    ("attention_2", 0, dict(heads=6, kv_heads=1, dim=32, vdim=128, mask={"size": 100}, diff=0.8)),
+    ("attention_2", 0, dict(heads=1, kv_heads=1, dim=3, vdim=5, mask={"size": 1})),
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_layer_alone(lib, kind, ff, kw, dtype):
+    if dtype == torch.bfloat16 and kw.get("vdim", 8) <= 5:
+        pytest.skip("heads of a few elements: a single 16-bit rounding is most of the value, nothing averages out")
+    cfg = make_cfg([layer(kind, ff, **kw)])
+    w = random_tensors(cfg, seed=3)
+    t = toks(150, cfg["vocab"], 1)
+    d = Driver(cfg, w, dtype, trace=True)
+    d.step([("a", t[:90])]), d.step([("a", t[90:])])
+    tr = []
+    want = R.forward(cfg, w, t, D64, tr).numpy()
+    resid = d.runner.trace[0, :60].cpu().numpy()                       # the second step's rows are tokens 90 .. 149
+    assert np.abs(resid - tr[0].numpy()[90:]).max() <= tol_of(dtype) * np.abs(tr[0].numpy()).max()
+    assert rel_err(d.result("a"), want) <= tol_of(dtype)
+
+
+# ------------------------------------------------------------------ edges and far keys in whole models
+@pytest.mark.parametrize("where", ["prompt", "decoded"])
+def test_chunk_edges_show_in_logits(lib, where):
+    """A one-layer model with chunks of 37: the plain model's logits at the first position of the second chunk differ
+    from those of a model whose chunks are one longer by far more than the tolerance (position 37 either starts afresh
+    or still sees 37 keys), and the framework follows the right one, in a prompt portion and for a token decoded alone."""
+    size = 37
+    cfg = make_cfg([layer("attention_2", 0, mask={"size": size})])
+    late = make_cfg([layer("attention_2", 0, mask={"size": size + 1})])
+    w = random_tensors(cfg, seed=4)
+    t = toks(2 * size + 5, cfg["vocab"], 5)
+    want, other = ref_logits(cfg, w, t), ref_logits(late, w, t)
+    assert rel_err(want[size:size + 1], other[size:size + 1]) > 50 * F32_TOL
+    assert rel_err(want[:size], other[:size]) < 1e-12
+    d = Driver(cfg, w, torch.float32)
+    if where == "prompt":
+        d.step([("a", t[:size - 1])]), d.step([("a", t[size - 1:])])
+    else:
+        d.step([("a", t[:size])])
+        for x in t[size:]:
+            d.step([("a", [x])])
+    assert rel_err(d.result("a"), want) <= F32_TOL
+
+
+@pytest.mark.parametrize("kind", ["attention", "channel_delta"])
+def test_a_far_token_shows_in_logits(lib, kind):
+    """Replacing the very first token of a 300-token prompt changes the last row's logits of the plain model by far more
+    than the tolerance, and the framework follows, the last row decoded alone after portions that end at and just after a
+    page border.  Attention: the last token equals the first, the key projection is the first head's query projection,
+    the two rotated entries of a head have a norm weight of zero and nothing is shifted, so the last query's score
+    against the first key is |q|^2, far above the scores of the random keys in between; the first value arrives turned by the whole distance.
+    Delta rule: decays of almost one, so the first token's write is still in the state at the end."""
+    if kind == "attention":
+        cfg = make_cfg([layer(kind, 0, heads=2, kv_heads=1, dim=64, vdim=16, scale=1.0, softcap=0.0,
+                              rot={"base": 100.0, "dims": 2})])
+        w = random_tensors(cfg, seed=11)
+        w["l0.shift"] = torch.zeros_like(w["l0.shift"])
+        w["l0.mix.q.norm"][:2] = 0.0                                  # the two rotated entries stay out of the scores
+        w["l0.mix.k"], w["l0.mix.k.norm"] = w["l0.mix.q"][:64].clone(), w["l0.mix.q.norm"].clone()
+    else:
+        cfg = make_cfg([layer(kind, 0)])
+        w = random_tensors(cfg, seed=11)
+        w["l0.mix.dt_bias"] = torch.full_like(w["l0.mix.dt_bias"], -12.0)
+        w["l0.mix.a2"] = torch.zeros_like(w["l0.mix.a2"])
+    n = 300
+    base = toks(n, cfg["vocab"] - 1, 5)
+    base[-1] = cfg["vocab"] - 1
+    t = list(base)
+    t[0] = cfg["vocab"] - 1
+    want, other = ref_logits(cfg, w, t), ref_logits(cfg, w, base)
+    assert rel_err(want[-1:], other[-1:]) > 50 * F32_TOL
+    d = Driver(cfg, w, torch.float32)
+    d.step([("a", t[:64])]), d.step([("a", t[64:129])]), d.step([("a", t[129:n - 1])]), d.step([("a", t[n - 1:])])
+    assert rel_err(d.result("a"), want) <= F32_TOL
+
+
+def test_layers_that_share_pages(lib):
+    """Two layers read the keys and values of a third with their own queries, masks and constants; a model in which
+    the reading layer's mask were the writing layer's gives other logits."""
+    cfg = make_cfg([layer("attention_2", 24), layer("attention_2", 0, kv_from=0, mask={"size": 50}, diff=0.6, scale=0.4),
+                    layer("channel_delta", 0), layer("attention_2", 30, kv_from=0, mask={"size": 7})])
+    w = random_tensors(cfg, seed=6)
+    t = toks(140, cfg["vocab"], 7)
+    want = ref_logits(cfg, w, t)
+    same_mask = json.loads(json.dumps(cfg))
+    same_mask["layers"][3]["mixer"]["mask"]["size"] = 37
+    assert rel_err(want, ref_logits(same_mask, w, t)) > 50 * F32_TOL
+    for dtype in (torch.float32, torch.bfloat16):
+        d = Driver(cfg, w, dtype)
+        d.step([("a", t[:70])]), d.step([("a", t[70:72])])
+        for x in t[72:]:
+            d.step([("a", [x])])
+        assert rel_err(d.result("a"), want) <= tol_of(dtype)
+
+
+# ------------------------------------------------------------------ schedules
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_whole_decode_and_portions_agree_with_the_plain_model(lib, dtype):
+    cfg = full_cfg()
+    w = random_tensors(cfg, seed=7)
+    t = toks(150, cfg["vocab"], 3)
+    want = ref_logits(cfg, w, t)
+    tol = tol_of(dtype)
+    d = Driver(cfg, w, dtype)
+    d.step([("whole", t)])
+    assert rel_err(d.result("whole"), want) <= tol
+    d.close("whole")
+    d.step([("dec", t[:60])])
+    for x in t[60:]:
+        d.step([("dec", [x])])
+    assert rel_err(d.result("dec"), want) <= tol
+    d.close("dec")
+    cuts = [2, 1, 2, 61, 2, 3, 64, 2, 13]                            # 150 tokens; cuts inside and at the ends of pages and chunks
+    at = 0
+    for c in cuts:
+        d.step([("cut", t[at:at + c])])
+        at += c
+    assert at == len(t)
+    assert rel_err(d.result("cut"), want) <= tol
+    if dtype == torch.float32:                                       # the cut must not matter beyond rounding
+        assert rel_err(d.result("cut"), d.result("dec")) <= 2e-5
+
+
+def test_unequal_batches_and_reuse_of_pages_and_slots(lib):
+    cfg = full_cfg()
+    w = random_tensors(cfg, seed=9)
+    V = cfg["vocab"]
+    reqs = {"a": toks(130, V, 1), "b": toks(3, V, 2), "c": toks(70, V, 3), "d": toks(65, V, 4), "e": toks(40, V, 5),
+            "f": toks(129, V, 6)}
+    want = {k: ref_logits(cfg, w, v) for k, v in reqs.items()}
+    d = Driver(cfg, w, torch.float32, num_blocks=7, max_seqs=4, slots=4)      # 7 pages: a(3) + c(2) + d(2) fill it
+    at = {k: 0 for k in reqs}
+
+    def portion(k, n):
+        p = (k, reqs[k][at[k]:at[k] + n])
+        at[k] += n
+        return p
+
+    d.step([portion("a", 64), portion("b", 2)])
+    d.step([portion("a", 1), portion("b", 1), portion("c", 30)])
+    d.close("b")                                                      # its page and slot go back
+    d.step([portion("c", 40), portion("a", 2), portion("d", 65)])
+    d.step([portion("a", 63)])
+    d.close("a"), d.close("c")
+    assert d.sched.num_free_blocks == 5 and d.sched.num_free_state_slots == 3
+    d.step([portion("e", 39), portion("f", 128)])                     # reuses a's and c's pages and slots
+    d.step([portion("f", 1), portion("e", 1)])
+    for k in "abcdef":
+        assert at[k] == len(reqs[k])
+        assert rel_err(d.result(k), want[k]) <= F32_TOL, k
+
+
+def test_first_tokens_and_long_decoding(lib):
+    cfg = full_cfg()
+    w = random_tensors(cfg, seed=13)
+    t = toks(260, cfg["vocab"], 8)
+    want = ref_logits(cfg, w, t)
+    d = Driver(cfg, w, torch.float32)
+    for x in t:                                                       # every token alone, from the very first
+        d.step([("a", [x])])
+    got = d.result("a")
+    assert rel_err(got[:6], want[:6]) <= F32_TOL
+    assert rel_err(got, want) <= F32_TOL
+
+
+def test_other_sizes(lib):
+    """Sizes of one and values that coincide elsewhere: one head, as many key / value heads as query heads, no grouping in
+    the delta rule, a rotation over two entries only, no score cap, no frequency scaling, chunks of one position, low
+    ranks of one, a convolution of one tap, a feed-forward of one unit, a factor of one on the sublayers, diff = 0."""
+    cfg = make_cfg([layer("attention", 7, heads=1, kv_heads=1, dim=2, vdim=2, scale=1.0, softcap=0.0,
+                          rot={"base": 2.0, "dims": 2}),
+                    layer("attention_2", 1, heads=1, kv_heads=1, dim=1, vdim=130, mask={"size": 1}, diff=0.0),
+                    layer("channel_delta", 0, heads=7, kv_heads=7, dim=1, vdim=5, conv=1, a_rank=1, g_rank=1),
+                    layer("attention_2", 0, kv_from=1, heads=1, kv_heads=1, dim=1, vdim=130, mask={"size": 1000}, diff=0.0),
+                    layer("attention", 130, heads=7, kv_heads=7, dim=8, vdim=6, rot={"base": 10000.0, "dims": 4}),
+                    layer("channel_delta", 3, heads=3, kv_heads=1, dim=130, vdim=1, conv=8, a_rank=2, g_rank=2)],
+                   width=24, vocab=50, eps=1e-3, mult=1.0)
+    w = random_tensors(cfg, seed=17)
+    t = toks(80, cfg["vocab"], 9)
+    want = ref_logits(cfg, w, t)
+    d = Driver(cfg, w, torch.float32)
+    d.step([("a", t[:7])]), d.step([("a", t[7:9])]), d.step([("a", t[9:])])
+    assert rel_err(d.result("a"), want) <= F32_TOL
+
+
+def test_greedy_generation_through_the_engine(lib):
+    """LLMEngine (schedule -> chunked prefill -> decode, state slots from the scheduler) against greedy decoding with
+    the plain model."""
+    from vllm_rs_b200 import engine, models
+    cfg = full_cfg()
+    w = random_tensors(cfg, seed=21)
+    V = cfg["vocab"]
+    prompts = [toks(75, V, 1), toks(5, V, 2), toks(40, V, 3)]
+    new = 12
+    runner = models.build_runner(cfg, w, dtype=torch.float32, device="cuda", num_blocks=12, max_blocks_per_seq=4,
+                                 max_seqs=5, max_tokens=64, num_state_slots=5)
+    eng = engine.LLMEngine(runner, 12, 3, chunk_size=32)              # prompts longer than a chunk are cut
+    sids = [eng.add_request(p, new) for p in prompts]
+    out = eng.run_to_completion()
+    for sid, p in zip(sids, prompts):
+        seq, want = list(p), []
+        for _ in range(new):
+            lg = ref_logits(cfg, w, seq)[-1]
+            top2 = np.sort(lg)[-2:]
+            nxt = int(lg.argmax())
+            want.append(nxt)
+            seq.append(nxt)
+            if top2[1] - top2[0] < 1e-3:                              # a near tie may flip in fp32: stop comparing there
+                break
+        assert out[sid][:len(want)] == want
+    assert eng.sched.num_free_state_slots == 5
+
+
+# ------------------------------------------------------------------ random configurations under random schedules
+@pytest.mark.parametrize("seed", [11, 12, 13, 14, 15, 16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_random_configurations_under_random_schedules(lib, seed, dtype):
+    """Sizes, layer orders and constants drawn at random (odd sizes, groups wider than an MMA tile, partial rotations,
+    chunks of 1 .. 129 positions, layers that read an earlier layer's pages); five requests of 5 .. 420 tokens share four
+    state slots and just enough pages, so both are used again."""
+    rng = np.random.default_rng(seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]              # noqa: E731
+    cfg = make_cfg(random_layers(rng, int(rng.integers(2, 7))), width=pick(64, 128, 200), vocab=pick(300, 512),
+                   eps=pick(1e-6, 1e-5), mult=pick(0.5, 1.0))
+    w = random_tensors(cfg, seed=seed)
+    reqs = {f"r{i}": toks(pick(5, 40, 150, 260, 420), cfg["vocab"], seed + i) for i in range(5)}
+    pages = sum(sorted((len(v) + 63) // 64 for v in reqs.values())[-4:])
+    d = Driver(cfg, w, dtype, num_blocks=pages, max_seqs=4, slots=4)
+    for st, ends in random_schedule(rng, reqs):
+        d.step(st)
+        for k in ends:
+            d.close(k)
+    want = {k: ref_logits(cfg, w, v) for k, v in reqs.items()}
+    for k in reqs:
+        assert rel_err(d.result(k), want[k]) <= tol_of(dtype), (k, [L["type"] for L in cfg["layers"]])
+
+
+# ------------------------------------------------------------------ a model folder through the command line
+def _write_model_folder(path, cfg, tensors):
+    """config.json and model.safetensors (8-byte little-endian header length, JSON header, raw data), bf16 tensors."""
+    header, blobs, at = {}, [], 0
+    for name, t in tensors.items():
+        raw = t.contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    with open(path / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+    with open(path / "config.json", "w") as f:
+        json.dump(cfg, f)
+
+
+def test_model_folder_through_trace_runner_and_generate(lib, tmp_path):
+    """The registry picks the model by config.json; the trace runner replays two interleaved requests on a pool of
+    three pages (the second request reuses the first one's page and slot), `generate` decodes greedily."""
+    root = Path(__file__).resolve().parent.parent
+    cfg = full_cfg()
+    w = random_tensors(cfg, seed=23)
+    assert all(t.dtype == torch.bfloat16 for t in w.values())
+    _write_model_folder(tmp_path, cfg, w)
+    V = cfg["vocab"]
+    a, b, c = toks(70, V, 1), toks(9, V, 2), toks(64, V, 3)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": [0, 39]}, {"id": "b", "tokens": b[:2], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[2:], "want": [6]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[40:69], "want": [28]}, {"id": "c", "tokens": c, "want": [63]}], "end": ["c"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[69:], "want": [0]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps), text=True,
+                       capture_output=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.split("\n") if ln.startswith("done")] == [f"done {i}" for i in range(4)]
+    ra, rb, rc = ref_logits(cfg, w, a), ref_logits(cfg, w, b), ref_logits(cfg, w, c)
+    want = {0: ra[[0, 39]], 1: rb[[8]], 2: np.stack([ra[68], rc[63]]), 3: ra[[69]]}
+    for i, ref in want.items():
+        got = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+        assert rel_err(got, ref) <= 2 * F32_TOL, i
+    r = subprocess.run([sys.executable, "-m", "vllm_rs_b200", "generate", "--model", str(tmp_path), "--dtype", "float32",
+                        "--prompt-ids", ",".join(map(str, b)), "--max-new-tokens", "5"], cwd=root, text=True,
+                       capture_output=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = json.loads(r.stdout.strip().split("\n")[-1])["output_ids"]
+    seq = list(b)
+    for k in range(5):
+        lg = ref_logits(cfg, w, seq)[-1]
+        top2 = np.sort(lg)[-2:]
+        if top2[1] - top2[0] < 1e-3:
+            break
+        assert got[k] == int(lg.argmax()), k
+        seq.append(int(lg.argmax()))

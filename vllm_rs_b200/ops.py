@@ -493,26 +493,35 @@ def resid_add_rmsnorm(x, y, w, eps, w_offset=0.0):
     return x
 
 
-def _attn_options(head_norm=False, v_from_k=False, q_temp=None, dist_slopes=None, gate_elems=False):
+def _attn_options(head_norm=False, v_from_k=False, q_temp=None, dist_slopes=None, gate_elems=False, rot_half=False,
+                  rot_mag=1.0, v_rot_freq=None, v_heads=0, chunk=0, out_f32=False, no_cache=False):
     """b200_attn_options; q_temp = (coef, every) or None.  Keep the returned object alive during the call."""
     o = _lib.AttnOptions(head_norm=int(bool(head_norm)), v_from_k=int(bool(v_from_k)),
                          q_temp_every=int(q_temp[1]) if q_temp else 0, gate_elems=int(bool(gate_elems)),
                          q_temp_coef=float(q_temp[0]) if q_temp else 0.0,
-                         dist_slopes=dist_slopes.data_ptr() if dist_slopes is not None else None)
+                         dist_slopes=dist_slopes.data_ptr() if dist_slopes is not None else None,
+                         rot_half=int(bool(rot_half)), rot_mag=float(rot_mag),
+                         v_rot_freq=v_rot_freq.data_ptr() if v_rot_freq is not None else None, v_heads=int(v_heads),
+                         chunk=int(chunk), out_f32=int(bool(out_f32)), no_cache=int(bool(no_cache)))
     return o
 
 
 def window_attn_prep(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, k_cache, v_cache, *, heads,
-                     rot_dims, eps, head_norm=False, v_from_k=False, q_temp=None):
+                     rot_dims, eps, head_norm=False, v_from_k=False, q_temp=None, rot_half=False, rot_mag=1.0,
+                     v_rot_freq=None):
     """proj fp32 [T, >= heads dim + kv_heads (dim + vdim)] -> q fp32 [T, heads, dim]; writes the K / V cache rows
     (k_cache [blocks, 64, kv_heads, dim], v_cache [blocks, 64, kv_heads, vdim]).  head_norm: q_norm_w / k_norm_w are
     [dim] and every head is normed on its own; v_from_k: no v block, the raw key rows are the values; q_temp =
-    (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1)."""
-    _cuda(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, k_cache, v_cache)
+    (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1).  rot_half: rotary
+    pairs are (i, i + rot_dims / 2); rot_mag multiplies cos and sin; v_rot_freq f64 [vdim / 2]: the value rows are
+    rotated by their position over all of vdim.  The value cache may have fewer heads than the key cache (several score
+    maps over one set of values)."""
+    _cuda(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, k_cache, v_cache, v_rot_freq)
     T = proj.shape[0]
     G, dk, dv = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
     q = torch.empty(T, heads, dk, dtype=torch.float32, device=proj.device)
-    opt = _attn_options(head_norm, v_from_k, q_temp)
+    opt = _attn_options(head_norm, v_from_k, q_temp, rot_half=rot_half, rot_mag=rot_mag, v_rot_freq=v_rot_freq,
+                        v_heads=v_cache.shape[2])
     _lib.lib().b200_window_attn_prep_ex(_p(proj), proj.shape[1], _p(bias), _p(q_norm_w), _p(k_norm_w), _p(rot_freq),
                                         _p(positions), _p(slot_mapping), _p(q), _p(k_cache), _p(v_cache), T, heads, G, dk,
                                         dv, int(rot_dims), float(eps), _dt(k_cache.dtype), C.byref(opt), _stream())
@@ -521,16 +530,19 @@ def window_attn_prep(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_m
 
 
 def window_attn(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables, *, window, keep_first, scale,
-                softcap=0.0, split=True, dist_slopes=None):
-    """q fp32 [T, heads, dim] -> [T, heads, vdim] in the cache dtype; gate fp32 logits [T, heads] (one per head) or
-    [T, heads vdim] (one per output element) or None; dist_slopes fp32 [heads]: scores are lowered by slope (i - j)."""
+                softcap=0.0, split=True, dist_slopes=None, chunk=0, out_f32=False):
+    """q fp32 [T, heads, dim] -> [T, heads, vdim] in the cache dtype (fp32 with out_f32); gate fp32 logits [T, heads]
+    (one per head) or [T, heads vdim] (one per output element) or None; dist_slopes fp32 [heads]: scores are lowered by
+    slope (i - j); chunk > 0: position i sees j <= i of its own chunk only.  A value cache with fewer heads than the key
+    cache: key head g reads value head g % v_heads."""
     _cuda(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables, dist_slopes)
     T, H, dk = q.shape
     G, dv = k_cache.shape[2], v_cache.shape[3]
-    out = torch.empty(T, H, dv, dtype=k_cache.dtype, device=q.device)
+    out = torch.empty(T, H, dv, dtype=torch.float32 if out_f32 else k_cache.dtype, device=q.device)
     nbytes = _lib.lib().b200_window_attn_workspace_bytes(T, H, G, dv, int(window), int(keep_first)) if split else 0
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
-    opt = _attn_options(dist_slopes=dist_slopes, gate_elems=gate is not None and gate.shape[1] == H * dv and dv > 1)
+    opt = _attn_options(dist_slopes=dist_slopes, gate_elems=gate is not None and gate.shape[1] == H * dv and dv > 1,
+                        v_heads=v_cache.shape[2], chunk=chunk, out_f32=out_f32)
     _lib.lib().b200_window_attn_ex(_p(out), _p(q), _p(k_cache), _p(v_cache), _p(sink), _p(gate),
                                    gate.shape[1] if gate is not None else 0, _p(cu_seqlens_q), _p(context_lens),
                                    _p(block_tables), block_tables.shape[1], context_lens.shape[0], T, H, G, dk, dv,
@@ -566,5 +578,75 @@ def decay_attn(q, k, v, state, state_slots, cu_seqlens_q, context_lens, *, head_
                                _p(chan_decay), H * dk, float(q_scale), float(k_scale), int(bool(act)), _p(state),
                                _p(state_slots), _p(cu_seqlens_q), _p(context_lens), context_lens.shape[0], H, dk, dv,
                                _stream())
+    _lib.check()
+    return out
+
+
+def attn_finish(a, gate, positions, *, heads, maps=1, lam=0.0, v_rot_freq=None, rot_half=True, head_norm=False, eps=1e-6,
+                out_scale=1.0, dtype=torch.float32):
+    """a fp32 [T, maps * heads, vdim] (map after map) -> [T, heads, vdim] in `dtype`: a[map 0] - lam a[map 1] (maps == 2),
+    turned back by -position * v_rot_freq (f64 [vdim / 2] or None), RMS-normed per head without a weight (head_norm),
+    times out_scale, times the sigmoid of gate ([T, heads] or [T, heads vdim] or None)."""
+    _cuda(a, gate, positions, v_rot_freq)
+    T, dv = a.shape[0], a.shape[2]
+    out = torch.empty(T, heads, dv, dtype=dtype, device=a.device)
+    _lib.lib().b200_attn_finish(_p(out), _p(a), _p(gate), gate.shape[1] if gate is not None else 0,
+                                int(gate is not None and gate.shape[1] == heads * dv and dv > 1), _p(positions),
+                                _p(v_rot_freq), int(bool(rot_half)), int(maps), float(lam), int(bool(head_norm)), float(eps),
+                                float(out_scale), T, heads, dv, _dt(dtype), _stream())
+    _lib.check()
+    return out
+
+
+def stream_norm(x, w, bias, *, kind="dyntanh", alpha=1.0, eps=1e-6, w_offset=0.0, shift_w=None, shift_state=None,
+                state_slots=None, cu_seqlens_q=None, context_lens=None, dtype=torch.float32):
+    """x fp32 [T, D] -> norm(x) in `dtype`: kind "rms" (x / rms(x) * (w_offset + w)) or "dyntanh" (tanh(alpha x) w + b).
+    With shift_w the token shift follows: out[t] = n[t] + (n[t-1] - n[t]) * shift_w, n[t-1] from the row above or, for a
+    portion's first row, from shift_state [slots, D] (zeros at position 0); shift_state is updated."""
+    _cuda(x, w, bias, shift_w, shift_state, state_slots, cu_seqlens_q, context_lens)
+    T, D = x.shape
+    out = torch.empty(T, D, dtype=dtype, device=x.device)
+    _lib.lib().b200_stream_norm(_p(out), _p(x), _p(w), _p(bias), float(alpha), {"rms": 0, "dyntanh": 1}[kind], float(eps),
+                                float(w_offset), None, _p(shift_w), _p(shift_state), _p(state_slots), _p(cu_seqlens_q),
+                                _p(context_lens), context_lens.shape[0] if context_lens is not None else 0, T, D,
+                                _dt(dtype), _stream())
+    _lib.check()
+    return out
+
+
+def depth_mix(hist, w):
+    """hist fp32 [n, ...] (contiguous), w fp32 [n] -> sum_j w[j] hist[j]."""
+    _cuda(hist, w)
+    out = torch.empty_like(hist[0])
+    _lib.lib().b200_depth_mix(_p(out), _p(hist), hist[0].numel(), _p(w), hist.shape[0], hist[0].numel(), _stream())
+    _lib.check()
+    return out
+
+
+def channel_decay(low, w2, bias, a_log, period):
+    """low fp32 [T, rank], w2 fp32 [C, rank], bias fp32 [C], a_log fp32 [C / period] ->
+    exp(-exp(a_log[c / period]) softplus(bias + low w2^T)) fp32 [T, C]."""
+    _cuda(low, w2, bias, a_log)
+    T, C_ = low.shape[0], w2.shape[0]
+    out = torch.empty(T, C_, dtype=torch.float32, device=low.device)
+    _lib.lib().b200_lowrank_decay_ex(_p(out), _p(low), low.shape[1], _p(w2), _p(bias), 1.0, 1, _p(a_log), int(period), T, C_,
+                                     w2.shape[1], _stream())
+    _lib.check()
+    return out
+
+
+def delta_rule_chan(q, k, v, b_raw, decay, state, state_slots, cu_seqlens_q, context_lens):
+    """The gated delta rule with ready-made decays per head and key channel: q, k fp32 [T, kv_heads, dim], v
+    [T, heads, vdim], b_raw [T, heads], decay [T, heads, dim] -> o fp32 [T, heads, vdim]; state is read and updated."""
+    T, Hk, dk = q.shape
+    H, dv = v.shape[1], v.shape[2]
+    row = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), b_raw], 1).contiguous()
+    decay = decay.reshape(T, -1).contiguous()
+    _cuda(row, decay, state, state_slots, cu_seqlens_q, context_lens)
+    out = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
+    ld, e, base = row.shape[1], 4, row.data_ptr()
+    _lib.lib().b200_delta_rule_chan(_p(out), base, base + Hk * dk * e, base + 2 * Hk * dk * e, ld,
+                                    base + (2 * Hk * dk + H * dv) * e, ld, _p(decay), H * dk, _p(state), _p(state_slots),
+                                    _p(cu_seqlens_q), _p(context_lens), context_lens.shape[0], H, Hk, dk, dv, _stream())
     _lib.check()
     return out
