@@ -27,6 +27,12 @@ Configs (BASELINE.json `configs`):
                       operands, random weights) next to the Fidasun decoder of equal width and depth: prefill and decode
                       tokens/s of both, and each kernel alone with and without its new options
                       (vllm_rs_b200/bench_gibevik.py).
+  tasadra             the Tasadra decoder (pre-norm layers with dynamic-tanh norms, token shift and a depth-weighted
+                      average of the layers' results; attention with rotated values; the delta rule with a decay per key
+                      channel; differential attention under a chunked mask with pages shared between layers; ungated
+                      squared-ReLU feed-forwards; fp32 residual, bf16 operands, random weights) next to the Zalalix
+                      decoder of equal width and depth: prefill and decode tokens/s of both, and each kernel alone beside
+                      the like kernel of the other models (vllm_rs_b200/bench_tasadra.py).
 
 Keys of the JSON line:
   value  device-resident: step inputs already in HBM, K CUDA-graph replays of the SAME step (the same KV slot is
@@ -66,6 +72,7 @@ CONFIGS = {
     "fidasun": dict(model="fidasun", fmt="bf16", kind="hybrid", baseline=None, label="Fidasun hybrid decoder"),
     "zalalix": dict(model="zalalix", fmt="bf16", kind="hybrid", baseline=None, label="Zalalix decoder"),
     "gibevik": dict(model="gibevik", fmt="bf16", kind="hybrid", baseline=None, label="Gibevik decoder"),
+    "tasadra": dict(model="tasadra", fmt="bf16", kind="hybrid", baseline=None, label="Tasadra decoder"),
     "l70_tp8": dict(model="llama3-70b", fmt="awq", kind="serve", gpus=8, max_num_seqs=64, requests=96,
                     prompt=(512, 2048), max_tokens=64, mean_gap_steps=1.0, baseline="configs[4]",
                     label="Llama-3-70B AWQ-int4"),
@@ -89,7 +96,7 @@ def parse():
     ap.add_argument("--no-extra-configs", action="store_true", help="N = 4 / 8: skip the q72_tp4 / l70_tp8 legs")
     ap.add_argument("--py-step", action="store_true",
                     help="e2e: drive the step from Python over the individual C symbols instead of b200_engine_step")
-    ap.add_argument("--size", default="w2048,w4096", help="--config fidasun / zalalix / gibevik: layer sizes, comma separated")
+    ap.add_argument("--size", default="w2048,w4096", help="--config fidasun / zalalix / gibevik / tasadra: layer sizes, comma separated")
     ap.add_argument("--dense-arm", action="store_true",
                     help="--config fidasun: also time the dense fp16 plan of equal size now (time-limited process)")
     ap.add_argument("--prefill-tokens", type=int, default=8192,
@@ -771,10 +778,13 @@ def run_b200(args):
     elif c["kind"] == "hybrid":
         if cx.world != 1:
             raise SystemExit(f"--config {cfgname} is a single-GPU configuration")
-        from vllm_rs_b200 import _lib, bench_gibevik, bench_hybrid, bench_zalalix
+        from vllm_rs_b200 import _lib, bench_gibevik, bench_hybrid, bench_tasadra, bench_zalalix
         launches0 = _lib.lib().b200_launch_count()
         with ClockSampler(cx.local) as clk:
-            if cfgname == "gibevik":
+            if cfgname == "tasadra":
+                sizes = [bench_tasadra.run(sz, layers=args.layers or 4, prefill=4096, batch=args.batch, ctx=2048,
+                                           reps=max(args.steps // 4, 3)) for sz in args.size.split(",")]
+            elif cfgname == "gibevik":
                 sizes = [bench_gibevik.run(sz, layers=args.layers or 4, prefill=4096, batch=args.batch, ctx=2048,
                                            reps=max(args.steps // 4, 3)) for sz in args.size.split(",")]
             elif cfgname == "zalalix":
