@@ -739,6 +739,9 @@ void b200_window_attn(void* out, const float* q, const void* k_cache, const void
                       float scale, float softcap, int32_t dt, void* workspace, int64_t stream);
 int64_t b200_window_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t vdim,
                                          int32_t window, int32_t keep_first);
+/* the same for a value cache of v_heads heads (b200_attn_options.v_heads) */
+int64_t b200_window_attn_workspace_bytes_ex(int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t v_heads,
+                                            int32_t vdim, int32_t window, int32_t keep_first);
 /* Further options of the two calls above (a zeroed struct = the plain calls).
  *   head_norm   != 0: q_norm_w / k_norm_w are fp32 [dim], shared by all heads, and every head is RMS-normed on its own
  *   v_from_k    != 0: the projection row has no v block; the value row is a copy of the raw key row (bias added, before

@@ -263,6 +263,7 @@ _SIGS = {
     "b200_window_attn_prep": (None, [c_vp, c_i32] + [c_vp] * 9 + [c_i32] * 6 + [c_f32, c_i32, c_i64]),
     "b200_window_attn": (None, [c_vp] * 6 + [c_i32] + [c_vp] * 3 + [c_i32] * 9 + [c_f32, c_f32, c_i32, c_vp, c_i64]),
     "b200_window_attn_workspace_bytes": (c_i64, [c_i32] * 6),
+    "b200_window_attn_workspace_bytes_ex": (c_i64, [c_i32] * 7),
     "b200_window_attn_prep_ex": (None, [c_vp, c_i32] + [c_vp] * 9 + [c_i32] * 6 + [c_f32, c_i32, C.POINTER(AttnOptions), c_i64]),
     "b200_window_attn_ex": (None, [c_vp] * 6 + [c_i32] + [c_vp] * 3 + [c_i32] * 9 + [c_f32, c_f32, c_i32, c_vp,
                                                                                     C.POINTER(AttnOptions), c_i64]),

@@ -166,7 +166,8 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
       if (needs_finish(l)) conv_n = std::max<size_t>(conv_n, static_cast<size_t>(maps) * l.heads * l.vdim);
       for (size_t rows = 1; rows <= r->attn_ws_rows; ++rows)
         attn_bytes = std::max(attn_bytes, window_attn_workspace_bytes(static_cast<int>(rows), maps * l.heads,
-                                                                      maps * l.kv_heads, l.vdim, l.window, l.keep_first));
+                                                                      maps * l.kv_heads, l.vdim, l.window, l.keep_first,
+                                                                      l.kv_heads));
     } else if (l.mixer == B200_MIXER_DECAY_ATTN) {
       aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.vdim);
       opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);

@@ -114,7 +114,8 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
                         const uint32_t* block_tables, int max_blocks, int num_seqs, int T, int heads, int kv_heads,
                         int dim, int vdim, int window, int keep_first, float scale, float softcap, int dt,
                         void* workspace, const b200_attn_options* opt, cudaStream_t st);
-size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first);
+// v_heads (0: kv_heads): heads of the value cache where several score maps share the values
+size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first, int v_heads = 0);
 // the combination of score maps, the turn back of rotated values, the per-head norm, scale and gate (see b200_attn_finish)
 void launch_attn_finish(void* out, const float* a, const float* gate, int ld_gate, int gate_elems,
                         const int64_t* positions, const double* v_rot_freq, int rot_half, int maps, float lambda,

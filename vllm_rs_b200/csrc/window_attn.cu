@@ -88,9 +88,10 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
       vsn[i] = static_cast<float>(s);
     }
   float inv_q = 1.f, inv_k = 1.f;
+  const bool with_k = k_cache != nullptr;          // a row of queries only has no key block to norm
   if (head_norm) {                       // every q and k head on its own: a warp per head
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int hh = warp; hh < heads + kv_heads; hh += nw) {
+    for (int hh = warp; hh < heads + (with_k ? kv_heads : 0); hh += nw) {
       const bool isq = hh < heads;
       const float* src = isq ? qr + hh * dim : kr + (hh - heads) * dim;
       const float* b = isq ? (bq ? bq + hh * dim : nullptr) : (bk ? bk + (hh - heads) * dim : nullptr);
@@ -111,7 +112,7 @@ __global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, 
     ss = block_sum(ss, red);
     inv_q = 1.f / sqrtf(ss / static_cast<float>(nq) + eps);
   }
-  if (!head_norm && k_norm_w) {
+  if (!head_norm && k_norm_w && with_k) {
     float ss = 0.f;
     for (int d = threadIdx.x; d < nk; d += blockDim.x) {
       const float v = kr[d] + (bk ? bk[d] : 0.f);
@@ -370,7 +371,9 @@ __device__ __forceinline__ uint32_t wpack_bf16(float lo, float hi) {
 // heads of ONE key / value head's group at one token -- they share the K and V rows, so one pass over the cache serves
 // them all -- and blockIdx.z owns a contiguous run of tiles of the token's visible keys (kept tokens first, then the
 // window); with nsplit > 1 the unnormalised parts go to part_o / part_ml and window_attn_merge_kernel finishes the
-// softmax (it adds the sink and the gate).
+// softmax (it adds the sink and the gate).  Where several score maps share one set of values (kv_heads = maps x
+// v_heads), the rows of a block are the group's heads under EVERY map (map after map): the K tiles of all maps are
+// staged, each map's scores are computed against its own keys, and the V tile is read once for all of them.
 template <int NT, bool HROWS>
 __global__ void __launch_bounds__(128)
 window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ q,
@@ -383,21 +386,24 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
                        int gate_elems, int chunk, int v_heads, int out_f32) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int P = dim + 8, PV = vdim + 8;                   // row pitches in bf16 elements (16-byte multiples)
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [WKT][P]
-  __nv_bfloat16* Vs = Ks + static_cast<size_t>(WKT) * P;                    // [WKT][PV]
+  // maps whose K tiles a block stages: all of them in the heads-as-rows form, the one of the block's head otherwise
+  const int maps = HROWS ? kv_heads / v_heads : 1;
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [maps][WKT][P]
+  __nv_bfloat16* Vs = Ks + static_cast<size_t>(maps) * WKT * P;             // [WKT][PV]
   __nv_bfloat16* Qs = Vs + static_cast<size_t>(WKT) * PV;                   // [WQ][P]
   float* Ss = reinterpret_cast<float*>(Qs + static_cast<size_t>(WQ) * P);   // [WQ][WKT + 1]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const int per_group = heads / kv_heads;
-  int b = -1, row0 = 0, nrows = 0, h = blockIdx.y, kvh = 0;
-  if (HROWS) {                                   // one token; heads [h, h + nrows) of key / value head kvh
-    const int rounds = (per_group + WQ - 1) / WQ;
+  int b = -1, row0 = 0, nrows = 0, h = blockIdx.y, kvh = 0, nh = 1;
+  if (HROWS) {          // one token; nh heads of value head kvh's group under every map: row r = map (r / nh), head h + r % nh
+    const int hpg = min(per_group, WQ / maps), rounds = (per_group + hpg - 1) / hpg;
     row0 = blockIdx.x;
     b = seq_of_row(cu, num_seqs, row0);
-    kvh = blockIdx.y / rounds;
-    const int first_in_group = (blockIdx.y % rounds) * WQ;
+    kvh = blockIdx.y / rounds;                   // (the value head; map m reads key head m * v_heads + kvh)
+    const int first_in_group = (blockIdx.y % rounds) * hpg;
     h = kvh * per_group + first_in_group;
-    nrows = min(WQ, per_group - first_in_group);
+    nh = min(hpg, per_group - first_in_group);
+    nrows = nh * maps;
   } else {                                       // 16 token rows of one sequence (tiles never straddle sequences)
     int acc = 0;
     for (int s = 0; s < num_seqs; ++s) {
@@ -418,16 +424,19 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
   const int pos_last = HROWS ? pos0 : pos0 + nrows - 1;
   const int key_lo = first_visible(pos0, window, chunk);               // first key of the window of the first row
   const int vh = kvh % v_heads;                                         // the value head this key head reads
+  // heads-as-rows: the query head of row r (the heads of map m are m * heads / maps ..)
+  auto head_of = [&](int r) { return (r / nh) * (heads / maps) + h + r % nh; };
   for (int e = threadIdx.x; e < WQ * dim; e += blockDim.x) {
     const int r = e / dim, d = e % dim;
-    const size_t qrow = HROWS ? static_cast<size_t>(row0) * heads + h + r : static_cast<size_t>(row0 + r) * heads + h;
+    const size_t qrow = HROWS ? static_cast<size_t>(row0) * heads + head_of(min(r, nrows - 1))
+                              : static_cast<size_t>(row0 + r) * heads + h;
     const float v = r < nrows ? q[qrow * dim + d] : 0.f;
     Qs[r * P + d] = __float2bfloat16_rn(v);
   }
   float m[2], l[2], slope[2];
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
-    const int hh = HROWS ? min(h + g + rr * 8, heads - 1) : h;
+    const int hh = HROWS ? head_of(min(g + rr * 8, nrows - 1)) : h;
     const bool with_sink = sink && nsplit == 1;            // split runs add the sink when the parts are merged
     m[rr] = with_sink ? sink[hh] : -1e30f;
     l[rr] = with_sink ? 1.f : 0.f;
@@ -452,15 +461,15 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
     const int kvec = dim / 8, vvec = vdim / 8;
     // key j of tile row k (head rows: the k-th visible key of the run); rows past the run are zero
     auto tile_key = [&](int k) { return HROWS ? vis.key(min(j0 + k, t_end - 1)) : j0 + k; };
-    for (int e = threadIdx.x; e < WKT * kvec; e += blockDim.x) {
-      const int k = e / kvec, d = (e % kvec) * 8;
+    for (int e = threadIdx.x; e < maps * WKT * kvec; e += blockDim.x) {
+      const int mp = e / (WKT * kvec), k = (e / kvec) % WKT, d = (e % kvec) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (j0 + k < t_end) {
         const int j = tile_key(k);
         const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
-        v = *reinterpret_cast<const uint4*>(k_cache + (slot * kv_heads + kvh) * dim + d);
+        v = *reinterpret_cast<const uint4*>(k_cache + (slot * kv_heads + (HROWS ? mp * v_heads + kvh : kvh)) * dim + d);
       }
-      *reinterpret_cast<uint4*>(Ks + static_cast<size_t>(k) * P + d) = v;
+      *reinterpret_cast<uint4*>(Ks + (static_cast<size_t>(mp) * WKT + k) * P + d) = v;
     }
     for (int e = threadIdx.x; e < WKT * vvec; e += blockDim.x) {
       const int k = e / vvec, d = (e % vvec) * 8;
@@ -473,27 +482,30 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
       *reinterpret_cast<uint4*>(Vs + static_cast<size_t>(k) * PV + d) = v;
     }
     __syncthreads();
-    // scores of keys [16 warp, 16 warp + 16)
-    float sc[2][4] = {};
-    for (int kk = 0; kk < dim; kk += 16) {
-      uint32_t a[4];
-      a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * P + kk + 2 * tq);
-      a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * P + kk + 2 * tq);
-      a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * P + kk + 2 * tq + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * P + kk + 2 * tq + 8);
+    // scores of keys [16 warp, 16 warp + 16): every map's keys against all rows, each row keeps its own map's
+    for (int mp = 0; mp < maps; ++mp) {
+      const __nv_bfloat16* Km = Ks + static_cast<size_t>(mp) * WKT * P;
+      float sc[2][4] = {};
+      for (int kk = 0; kk < dim; kk += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * P + kk + 2 * tq);
+        a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * P + kk + 2 * tq);
+        a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * P + kk + 2 * tq + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * P + kk + 2 * tq + 8);
 #pragma unroll
-      for (int nb = 0; nb < 2; ++nb) {
-        const __nv_bfloat16* kr = Ks + static_cast<size_t>(warp * 16 + nb * 8 + g) * P + kk + 2 * tq;
-        wmma_bf16_16816(sc[nb], a, *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+        for (int nb = 0; nb < 2; ++nb) {
+          const __nv_bfloat16* kr = Km + static_cast<size_t>(warp * 16 + nb * 8 + g) * P + kk + 2 * tq;
+          wmma_bf16_16816(sc[nb], a, *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+        }
       }
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const int r = g + (f >> 1) * 8, kcol = warp * 16 + nb * 8 + 2 * tq + (f & 1);
+          if (maps == 1 || r / nh == mp) Ss[r * (WKT + 1) + kcol] = cap_score(sc[nb][f] * scale, softcap);
+        }
     }
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-      for (int f = 0; f < 4; ++f) {
-        const int r = g + (f >> 1) * 8, kcol = warp * 16 + nb * 8 + 2 * tq + (f & 1);
-        Ss[r * (WKT + 1) + kcol] = cap_score(sc[nb][f] * scale, softcap);
-      }
     __syncthreads();
     // the same online softmax in every warp; this lane's P entries are exactly its A fragments
     float p[2][16];
@@ -563,7 +575,7 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
   for (int rr = 0; rr < 2; ++rr) {
     const int r = g + rr * 8;
     if (r >= nrows) continue;
-    const int hh = HROWS ? h + r : h;
+    const int hh = HROWS ? head_of(r) : h;
     const size_t trow = HROWS ? row0 : row0 + r;
     const size_t orow = trow * heads + hh;
     if (nsplit == 1) {
@@ -813,12 +825,19 @@ static bool window_rows_enabled() {
   }
   return v == 1;
 }
-static size_t window_mma_smem(int dim, int vdim) {
-  return static_cast<size_t>(WKT + WQ) * (dim + 8) * 2 + static_cast<size_t>(WKT) * (vdim + 8) * 2 +
+// maps: score maps whose K tiles a block stages (heads-as-rows form with several maps over one set of values)
+static size_t window_mma_smem(int dim, int vdim, int maps = 1) {
+  return static_cast<size_t>(maps * WKT + WQ) * (dim + 8) * 2 + static_cast<size_t>(WKT) * (vdim + 8) * 2 +
          static_cast<size_t>(WQ) * (WKT + 1) * 4;
 }
-static bool window_mma_shape_ok(int dim, int vdim) {
-  return dim % 16 == 0 && vdim % 32 == 0 && vdim <= 256 && window_mma_smem(dim, vdim) <= 200 * 1024;
+static bool window_mma_shape_ok(int dim, int vdim, int maps = 1) {
+  return dim % 16 == 0 && vdim % 32 == 0 && vdim <= 256 && maps <= WQ && window_mma_smem(dim, vdim, maps) <= 200 * 1024;
+}
+// blocks per token of the heads-as-rows form: a value head's group takes ceil(per_group / hpg) blocks
+static int window_mma_row_blocks(int heads, int kv_heads, int v_heads) {
+  const int maps = std::max(1, kv_heads / v_heads), per_group = heads / kv_heads;
+  const int hpg = std::max(1, std::min(per_group, WQ / std::min(maps, WQ)));
+  return v_heads * ((per_group + hpg - 1) / hpg);
 }
 
 static int window_attn_warps(int heads, int kv_heads) {
@@ -833,15 +852,16 @@ int window_attn_splits(int T, int heads, int kv_heads, int window, int keep_firs
   return std::max(1, std::min(n, 16));
 }
 // key splits of the heads-as-rows tensor-core form: four blocks per SM, at most one split per key tile, at most 16
-static int window_attn_mma_splits(int T, int heads, int kv_heads, int window, int keep_first) {
-  const int blocks = T * kv_heads * ((heads / kv_heads + WQ - 1) / WQ);
+static int window_attn_mma_splits(int T, int heads, int kv_heads, int window, int keep_first, int v_heads) {
+  const int blocks = T * window_mma_row_blocks(heads, kv_heads, v_heads);
   int n = (4 * sm_count() + blocks - 1) / blocks;
   if (window > 0) n = std::min(n, (window + std::max(keep_first, 0) + WKT - 1) / WKT);
   return std::max(1, std::min(n, 16));
 }
-size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first) {
+size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first, int v_heads) {
+  if (v_heads <= 0 || kv_heads % v_heads != 0) v_heads = kv_heads;
   const int n = std::max(window_attn_splits(T, heads, kv_heads, window, keep_first),
-                         window_attn_mma_splits(T, heads, kv_heads, window, keep_first));
+                         window_attn_mma_splits(T, heads, kv_heads, window, keep_first, v_heads));
   return n == 1 ? 0 : static_cast<size_t>(T) * heads * n * (vdim + 2) * 4;
 }
 
@@ -892,13 +912,13 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
     }
   }
   // bf16: the tensor-core kernel; steps of few rows take its heads-as-rows form with the keys split over blocks
-  if (!dt && window_mma_enabled() && window_mma_shape_ok(dim, vdim)) {
-    const bool hrows = T <= 2 * sm_count() / 4;
-    const size_t smem = window_mma_smem(dim, vdim);
-    const int nsplit = hrows && workspace ? window_attn_mma_splits(T, heads, kv_heads, window, keep_first) : 1;
+  const bool hrows = T <= 2 * sm_count() / 4;
+  if (!dt && window_mma_enabled() && window_mma_shape_ok(dim, vdim, hrows ? kv_heads / v_heads : 1)) {
+    const size_t smem = window_mma_smem(dim, vdim, hrows ? kv_heads / v_heads : 1);
+    const int nsplit = hrows && workspace ? window_attn_mma_splits(T, heads, kv_heads, window, keep_first, v_heads) : 1;
     float* part_o = reinterpret_cast<float*>(workspace);
     float* part_ml = part_o ? part_o + static_cast<size_t>(T) * heads * nsplit * vdim : nullptr;
-    const dim3 grid = hrows ? dim3(T, kv_heads * ((heads / kv_heads + WQ - 1) / WQ), nsplit)
+    const dim3 grid = hrows ? dim3(T, window_mma_row_blocks(heads, kv_heads, v_heads), nsplit)
                             : dim3((T + WQ - 1) / WQ + num_seqs, heads, 1);
 #define B200_WMMA2(NT, HR)                                                                                        \
   {                                                                                                                \
@@ -1112,6 +1132,11 @@ void b200_window_attn(void* out, const float* q, const void* k_cache, const void
 }
 int64_t b200_window_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t vdim,
                                          int32_t window, int32_t keep_first) {
-  return static_cast<int64_t>(b200::window_attn_workspace_bytes(num_tokens, heads, kv_heads, vdim, window, keep_first));
+  return static_cast<int64_t>(b200::window_attn_workspace_bytes(num_tokens, heads, kv_heads, vdim, window, keep_first, 0));
+}
+int64_t b200_window_attn_workspace_bytes_ex(int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t v_heads,
+                                            int32_t vdim, int32_t window, int32_t keep_first) {
+  return static_cast<int64_t>(b200::window_attn_workspace_bytes(num_tokens, heads, kv_heads, vdim, window, keep_first,
+                                                                v_heads));
 }
 }

@@ -539,7 +539,8 @@ def window_attn(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, blo
     T, H, dk = q.shape
     G, dv = k_cache.shape[2], v_cache.shape[3]
     out = torch.empty(T, H, dv, dtype=torch.float32 if out_f32 else k_cache.dtype, device=q.device)
-    nbytes = _lib.lib().b200_window_attn_workspace_bytes(T, H, G, dv, int(window), int(keep_first)) if split else 0
+    nbytes = _lib.lib().b200_window_attn_workspace_bytes_ex(T, H, G, v_cache.shape[2], dv, int(window),
+                                                            int(keep_first)) if split else 0
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
     opt = _attn_options(dist_slopes=dist_slopes, gate_elems=gate is not None and gate.shape[1] == H * dv and dv > 1,
                         v_heads=v_cache.shape[2], chunk=chunk, out_f32=out_f32)
