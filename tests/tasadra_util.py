@@ -107,13 +107,13 @@ def random_layers(rng, count):
         r = rng.random()
         if r < 0.35:
             G = pick(1, 2, 3)
-            dk = pick(8, 16, 32, 48, 72)
-            rot = {"base": pick(100.0, 10000.0, 500000.0), "dims": pick(2, dk // 2, dk) // 2 * 2}
+            dk = pick(8, 16, 32, 40, 80)
+            rot = {"base": pick(100.0, 10000.0, 1000000.0), "dims": pick(2, dk // 2, dk) // 2 * 2}
             if rng.random() < 0.6:
-                rot["scaling"] = {"factor": pick(2.0, 8.0), "original": pick(32, 128), "fast": pick(8.0, 32.0),
+                rot["scaling"] = {"factor": pick(2.0, 8.0), "original": pick(32, 128), "fast": pick(8.0, 16.0),
                                   "slow": pick(1.0, 2.0)}
             m = dict(heads=G * pick(1, 2, 4, 9), kv_heads=G, dim=dk, vdim=pick(8, 16, 32, 50, 96), scale=pick(0.125, 0.3),
-                     softcap=pick(0.0, 5.0, 50.0), rot=rot)
+                     softcap=pick(0.0, 5.0, 20.0), rot=rot)
             kind = "attention"
         elif r < 0.65:
             G = pick(1, 2)
@@ -123,7 +123,7 @@ def random_layers(rng, count):
         else:
             G = pick(1, 2)
             m = dict(heads=G * pick(1, 2, 4), kv_heads=G, dim=pick(8, 16, 32, 40), vdim=pick(8, 16, 32, 64, 80),
-                     scale=pick(0.2, 0.35), diff=pick(0.1, 0.5, 0.8), mask={"size": pick(1, 5, 64, 100, 129)})
+                     scale=pick(0.2, 0.35), diff=pick(0.1, 0.4, 0.8), mask={"size": pick(1, 5, 64, 100, 129)})
             if sources and rng.random() < 0.5:               # its own queries, mask and constants on another layer's pages
                 m["kv_from"] = pick(*sources)
                 m.update({n: layers[m["kv_from"]]["mixer"][n] for n in ("heads", "kv_heads", "dim", "vdim")})

@@ -43,7 +43,7 @@ def test_lambda_of_differential_attention():
 def test_frequency_tables_agree_with_the_plain_formulas():
     from vllm_rs_b200.rotary import rotary_frequencies
     for n, base, sc in ((16, 10000.0, None), (12, 300.0, {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}),
-                        (48, 500000.0, {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 2.0}), (2, 2.0, None)):
+                        (40, 1000000.0, {"factor": 8.0, "original": 1024, "fast": 16.0, "slow": 2.0}), (2, 2.0, None)):
         f, fac = rotary_frequencies(n, base, sc)
         rf, rfac = R.pair_frequencies(n, base, sc)
         assert np.allclose(f, rf.numpy(), rtol=1e-14) and math.isclose(fac, rfac, rel_tol=1e-14)

@@ -42,7 +42,7 @@ def config(size, layers):
            "channel_delta": dict(heads=de["heads"], kv_heads=de["kv_heads"], dim=de["dim"], vdim=de["vdim"], conv=de["conv"],
                                  a_rank=de["a_rank"], g_rank=de["g_rank"]),
            "attention_2": dict(heads=di["heads"], kv_heads=di["kv_heads"], dim=di["dim"], vdim=di["vdim"],
-                               scale=di["dim"] ** -0.5, diff=0.5, mask={"size": di["chunk"]})}
+                               scale=di["dim"] ** -0.5, diff=0.4, mask={"size": di["chunk"]})}
     out, source = [], None
     for i in range(layers):
         kind = ORDER[i % 4]
@@ -56,7 +56,7 @@ def config(size, layers):
         else:
             out.append({"type": kind, "mixer": mix[kind], "mlp": {"kind": "dense", "ff": s["ff"]}})
     return {"architecture": "Tasadra", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6},
-            "residual_mult": 0.5, "layers": out}
+            "residual_mult": 0.6, "layers": out}
 
 
 def random_tensors(cfg, seed=0):
