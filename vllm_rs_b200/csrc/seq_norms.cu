@@ -133,86 +133,52 @@ __global__ void relu2_f32_kernel(T* __restrict__ out, const float* __restrict__ 
   }
 }
 
-// A norm of the stream: RMS, or the dynamic tanh  tanh(alpha x) w + b  that needs no statistics.
-__device__ __forceinline__ float normed_entry(const float* row, int d, int kind, float inv, float alpha,
-                                              const float* __restrict__ w, const float* __restrict__ bias, float w_offset) {
-  return kind == B200_NORM_DYNTANH ? tanhf(alpha * row[d]) * w[d] + (bias ? bias[d] : 0.f) : row[d] * inv * (w_offset + w[d]);
-}
-__device__ __forceinline__ float row_inv_rms(const float* row, int width, float eps, float* red) {
-  float ss = 0.f;
-  for (int d = threadIdx.x; d < width; d += blockDim.x) ss += row[d] * row[d];
-  ss = block_sum(ss, red);
-  return 1.f / sqrtf(ss / static_cast<float>(width) + eps);
-}
-
-// One block per output row: out[r] = norm(x[row(r)]); rows == nullptr: row(r) = r.
+// One block per output row: a norm of the stream (RMS, or the dynamic tanh  tanh(alpha x) w + b  that needs no
+// statistics) and, with shift_w, the token shift behind it:  out[t] = n[t] + (n[t-1] - n[t]) * shift_w, where n[t-1] is
+// the un-shifted norm of the sequence's previous token -- recomputed from the row above, or, for the first row of a
+// portion, read from the sequence's shift state (zeros at position 0).  The block of a sequence's FIRST row also writes
+// the state: the un-shifted norm of the sequence's last row of the step.  Every thread reads the state entries it later
+// overwrites, so the portion's first row sees the old state whatever the order of the blocks.
 template <typename T>
 __global__ void stream_norm_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                                    const float* __restrict__ bias, float alpha, int kind, int width, float eps,
-                                   float w_offset, const uint32_t* __restrict__ rows) {
+                                   float w_offset, const uint32_t* __restrict__ rows, const float* __restrict__ shift_w,
+                                   float* __restrict__ shift_state, const int32_t* __restrict__ slots,
+                                   const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int num_seqs) {
   __shared__ float red[33];
   const int r = blockIdx.x;
-  const float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * width;
-  const float inv = kind == B200_NORM_DYNTANH ? 1.f : row_inv_rms(xr, width, eps, red);
-  for (int d = threadIdx.x; d < width; d += blockDim.x)
-    st(out + static_cast<size_t>(r) * width + d, normed_entry(xr, d, kind, inv, alpha, w, bias, w_offset));
-}
-
-// The norm with the token shift behind it:  out[t] = n[t] + (n[t-1] - n[t]) * shift_w, n the un-shifted norm, n[t-1] of a
-// sequence's first row in the step read from its shift state (zeros at position 0).  A block walks kShiftRows
-// consecutive rows, every thread its own entries, so the norm of a row is evaluated once and handed on as the next row's
-// n[t-1] (plus once more for the row above the block's first; steps of few rows take one row per block).  The block that holds a sequence's FIRST row of the step
-// also writes the sequence's new state, the un-shifted norm of its LAST row of the step: every thread first reads the
-// state entries it later overwrites, so the old state is seen whatever the order of the blocks.
-template <typename T, int kShiftRows>
-__global__ void stream_norm_shift_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
-                                         const float* __restrict__ bias, float alpha, int kind, int width, float eps,
-                                         float w_offset, const float* __restrict__ shift_w,
-                                         float* __restrict__ shift_state, const int32_t* __restrict__ slots,
-                                         const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int num_seqs,
-                                         int num_rows) {
-  __shared__ float red[33];
-  const int r0 = blockIdx.x * kShiftRows, nr = min(kShiftRows, num_rows - r0);
-  // facts of the block's rows, the same in every thread
-  int seq[kShiftRows], last[kShiftRows];
-  bool first[kShiftRows];
-  float inv[kShiftRows + 1], inv_last[kShiftRows];        // RMS kind: inv[0] of the row above, inv[i + 1] of row r0 + i
-#pragma unroll
-  for (int i = 0; i < kShiftRows; ++i) {
-    const int t = r0 + min(i, nr - 1);
-    seq[i] = seq_of_row(cu, num_seqs, t);
-    first[i] = t == static_cast<int>(cu[seq[i]]);
-    last[i] = static_cast<int>(cu[seq[i] + 1]) - 1;
-    inv[i + 1] = inv_last[i] = 1.f;
+  const int t = rows ? static_cast<int>(rows[r]) : r;
+  const float* xr = x + static_cast<size_t>(t) * width;
+  // inverse root mean square of a row (RMS kind only)
+  auto inv_rms = [&](const float* row) {
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) ss += row[d] * row[d];
+    ss = block_sum(ss, red);
+    return 1.f / sqrtf(ss / static_cast<float>(width) + eps);
+  };
+  auto normed = [&](const float* row, float inv, int d) {
+    return kind == B200_NORM_DYNTANH ? tanhf(alpha * row[d]) * w[d] + (bias ? bias[d] : 0.f)
+                                     : row[d] * inv * (w_offset + w[d]);
+  };
+  const float inv = kind == B200_NORM_DYNTANH ? 1.f : inv_rms(xr);
+  if (!shift_w) {
+    for (int d = threadIdx.x; d < width; d += blockDim.x) st(out + static_cast<size_t>(r) * width + d, normed(xr, inv, d));
+    return;
   }
-  inv[0] = 1.f;
-  if (kind != B200_NORM_DYNTANH) {
-    if (!first[0]) inv[0] = row_inv_rms(x + static_cast<size_t>(r0 - 1) * width, width, eps, red);
-    for (int i = 0; i < nr; ++i) {
-      inv[i + 1] = row_inv_rms(x + static_cast<size_t>(r0 + i) * width, width, eps, red);
-      if (first[i] && last[i] >= r0 + nr)
-        inv_last[i] = row_inv_rms(x + static_cast<size_t>(last[i]) * width, width, eps, red);
-    }
-  }
+  const int b = seq_of_row(cu, num_seqs, t);
+  const int t0 = static_cast<int>(cu[b]), t1 = static_cast<int>(cu[b + 1]);
+  const bool first = t == t0;
+  const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;          // the sequence starts in this step
+  float* sp = shift_state + static_cast<size_t>(slots[b]) * width;
+  const float* xp = xr - width;                                      // the row above (same sequence unless `first`)
+  const float* xl = x + static_cast<size_t>(t1 - 1) * width;         // the sequence's last row of the step
+  const float inv_p = (kind == B200_NORM_DYNTANH || first) ? 1.f : inv_rms(xp);
+  const float inv_l = (kind == B200_NORM_DYNTANH || !first) ? 1.f : (t1 - 1 == t ? inv : inv_rms(xl));
   for (int d = threadIdx.x; d < width; d += blockDim.x) {
-    const float sw = shift_w[d];
-    float prev = first[0] ? 0.f : normed_entry(x + static_cast<size_t>(r0 - 1) * width, d, kind, inv[0], alpha, w, bias, w_offset);
-#pragma unroll
-    for (int i = 0; i < kShiftRows; ++i) {
-      if (i >= nr) break;
-      const int t = r0 + i, b = seq[i];
-      const float n = normed_entry(x + static_cast<size_t>(t) * width, d, kind, inv[i + 1], alpha, w, bias, w_offset);
-      float* sp = shift_state + static_cast<size_t>(slots[b]) * width;
-      if (first[i]) {
-        const bool fresh = ctx[b] == cu[b + 1] - cu[b];              // the sequence starts in this step
-        prev = fresh ? 0.f : sp[d];
-        if (last[i] >= r0 + nr)                                      // its last row lies in a later block
-          sp[d] = normed_entry(x + static_cast<size_t>(last[i]) * width, d, kind, inv_last[i], alpha, w, bias, w_offset);
-      }
-      st(out + static_cast<size_t>(t) * width + d, n + (prev - n) * sw);
-      if (t == last[i] && static_cast<int>(cu[b]) >= r0) sp[d] = n;  // first and last row in this block
-      prev = n;
-    }
+    const float n = normed(xr, inv, d);
+    const float prev = first ? (fresh ? 0.f : sp[d]) : normed(xp, inv_p, d);
+    st(out + static_cast<size_t>(r) * width + d, n + (prev - n) * shift_w[d]);
+    if (first) sp[d] = t1 - 1 == t ? n : normed(xl, inv_l, d);
   }
 }
 
@@ -331,26 +297,12 @@ void launch_stream_norm(void* out, const float* x, const float* w, const float* 
                         const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int T, int width,
                         int dt, cudaStream_t st_) {
   if (T <= 0) return;
-  if (shift_w) {
-#define B200_SHIFT(TY, R)                                                                                             \
-  stream_norm_shift_kernel<TY, R><<<(T + R - 1) / R, 256, 0, st_>>>((TY*)out, x, w, bias, alpha, kind, width, eps,    \
-                                                                    w_offset, shift_w, shift_state, slots, cu, ctx,   \
-                                                                    num_seqs, T)
-    const bool many = T > 8 * sm_count();          // enough rows to fill the GPU with four of them per block
-    if (dt) {
-      if (many) B200_SHIFT(float, 4);
-      else B200_SHIFT(float, 1);
-    } else {
-      if (many) B200_SHIFT(__nv_bfloat16, 4);
-      else B200_SHIFT(__nv_bfloat16, 1);
-    }
-#undef B200_SHIFT
-  } else if (dt) {
-    stream_norm_kernel<float><<<T, 256, 0, st_>>>((float*)out, x, w, bias, alpha, kind, width, eps, w_offset, rows);
-  } else {
+  if (dt)
+    stream_norm_kernel<float><<<T, 256, 0, st_>>>((float*)out, x, w, bias, alpha, kind, width, eps, w_offset, rows, shift_w,
+                                                  shift_state, slots, cu, ctx, num_seqs);
+  else
     stream_norm_kernel<__nv_bfloat16><<<T, 256, 0, st_>>>((__nv_bfloat16*)out, x, w, bias, alpha, kind, width, eps, w_offset,
-                                                          rows);
-  }
+                                                          rows, shift_w, shift_state, slots, cu, ctx, num_seqs);
   B200_CUDA_LAUNCH_CHECK();
 }
 
