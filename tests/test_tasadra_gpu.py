@@ -170,7 +170,8 @@ def _plain_attention(q, k, v, rows_pos, scale, chunk, key_of, val_of):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("split", [True, False])
-@pytest.mark.parametrize("dk,dv,H,G,maps", [(12, 10, 4, 2, 1), (32, 32, 3, 1, 2), (16, 64, 4, 2, 2), (16, 16, 34, 2, 1)])
+@pytest.mark.parametrize("dk,dv,H,G,maps", [(12, 10, 4, 2, 1), (32, 32, 3, 1, 2), (16, 64, 4, 2, 2), (16, 16, 34, 2, 1),
+                                            (16, 32, 18, 1, 2)])       # the last: a group too wide for one MMA tile, under two maps
 def test_chunked_attention_op_edges(lib, dtype, split, dk, dv, H, G, maps):
     """Keys carry a position tag u and its square, so a query can put a sharp peak on any position.  Queries per row: a
     peak on the first key of the row's chunk (just inside), on the key before it (just outside: had the kernel seen it,
