@@ -763,7 +763,7 @@ typedef struct b200_attn_options {
    *                     back by its own position
    *   v_heads     > 0: the value cache has v_heads heads and key head g reads value head g % v_heads (several score
    *                     maps over one set of values: the maps' key heads are laid out map after map); 0: kv_heads
-   *   chunk       > 0: position i sees j <= i only if floor(i / chunk) == floor(j / chunk) (chunks count from position 0)
+   *   chunk       > 0: position i sees j <= i only if floor(i / chunk) == floor(j / chunk) (true positions, however a prompt is cut)
    *   out_f32     != 0: the attention writes fp32 whatever dt says (for b200_attn_finish)
    *   no_cache    != 0 (prep): the projection row holds queries only, nothing is written to a cache                  */
   int32_t rot_half;
