@@ -22,7 +22,8 @@
 //   * rotated values: the value row of position j is turned by j (all of vdim) before it is cached, and
 //     attn_finish_kernel turns a head's output back by its own position, so that a value enters the output turned by
 //     the distance between key and query
-//   * a chunked mask: position i sees j <= i only inside its own chunk of `chunk` positions (chunk c holds the true positions c * chunk .. c * chunk + chunk - 1, however a prompt is cut)
+//   * a chunked mask: position i sees j <= i only inside its own chunk of `chunk` positions (chunk c holds the true
+//     positions c * chunk .. c * chunk + chunk - 1, however a prompt is cut)
 //   * several score maps over one set of values (differential attention): the maps' query and key heads are laid out
 //     map after map, the value cache has v_heads heads and key head g reads value head g % v_heads; the maps' outputs
 //     are written in fp32 and attn_finish_kernel combines them (a_0 - lambda a_1), norms per head, scales and gates
